@@ -1,0 +1,243 @@
+// C ABI of libimmerdink_host.so: pure host queries over plan.hpp. Nothing here touches CUDA.
+// No exception leaves a function: allocation failures map to ALLOC_FAILED.
+#include <algorithm>
+#include <cstring>
+#include <new>
+
+#include "immerdink/immerdink_host.h"
+#include "plan.hpp"
+
+namespace {
+
+using imd::Analysis;
+using imd::ExecPlan;
+
+template <class F>
+imd_status_t guarded(F&& f) {
+  try {
+    return f();
+  } catch (const std::bad_alloc&) {
+    return IMD_STATUS_ALLOC_FAILED;
+  } catch (...) {
+    return IMD_STATUS_INVALID_VALUE;
+  }
+}
+
+bool any_packed(const imd_packing_t* p) { return p != nullptr && (p->A != nullptr || p->B != nullptr); }
+
+static_assert(sizeof(imd_tensor_t) == 32 && sizeof(imd_options_t) == 24, "ABI struct sizes");
+static_assert(sizeof(imd_region_t) == 16 && sizeof(imd_lowering_t) == 192, "ABI struct sizes");
+static_assert(offsetof(imd_lowering_t, fused) == 136 && offsetof(imd_lowering_t, sm_count) == 152 &&
+                  offsetof(imd_lowering_t, fused_large) == 168 &&
+                  offsetof(imd_lowering_t, packed) == 176 && offsetof(imd_lowering_t, k_align) == 184,
+              "imd_lowering_t version boundaries");
+static_assert(sizeof(imd_pack_desc_t) == 72 && sizeof(imd_pack_layout_t) == 136 &&
+                  sizeof(imd_packing_t) == 16,
+              "ABI struct sizes");
+static_assert(sizeof(imd_err_request_t) == 64 && sizeof(imd_err_t) == 72, "ABI struct sizes");
+
+imd_status_t lowering_impl(const imd_tensor_t* A, const imd_tensor_t* B, const imd_tensor_t* C,
+                           const imd_options_t* options, imd_lowering_t* out) {
+  if (out == nullptr || out->struct_size < 136) return IMD_STATUS_INVALID_VALUE;
+  imd_lowering_t r;
+  std::memset(&r, 0, sizeof r);
+  r.struct_size = out->struct_size;
+  const int32_t sms_in = out->struct_size >= 168 ? out->sm_count : 0;
+  if (sms_in < 0) return IMD_STATUS_INVALID_VALUE;
+  r.status = guarded([&]() -> imd_status_t {
+    Analysis an;
+    if (const imd_status_t st = imd::analyze(A, B, C, options, &an); st != IMD_STATUS_SUCCESS)
+      return st;
+    ExecPlan e;
+    const imd_status_t plan_st = imd::make_plan(an, &e);
+    r.lowered = 1;
+    r.num_moduli = e.N;
+    r.residue_group = e.g;
+    r.swapped = e.swapped ? 1 : 0;
+    r.m = e.m, r.n = e.n, r.k = e.k, r.b = e.b;
+    r.n_hat = e.n_hat, r.k_hat = e.k_hat;
+    r.k_align = e.k_align;
+    r.kappa = e.k >= 1 ? imd::ceil_sqrt_u64(static_cast<uint64_t>(e.k)) : 0;
+    r.workspace_bytes = an.layout.total;
+    r.dispatch = e.path == imd::Path::kNoop ? IMD_DISPATCH_NOOP
+                 : e.k == 0                 ? IMD_DISPATCH_SCALE
+                 : e.emulated()             ? IMD_DISPATCH_EMULATE
+                                            : IMD_DISPATCH_DIRECT;
+    if (e.path != imd::Path::kNoop) r.vec_entries = an.view.vec_entries();
+    if (r.dispatch == IMD_DISPATCH_EMULATE) {
+      r.num_groups = (e.N + e.g - 1) / e.g;
+      r.k_chunks = imd::plan_k_chunks(e);
+      r.gemm_launches = imd::plan_gemm_launches(e);
+    }
+    e.vec_resident = an.options.vec_mode == IMD_VEC_RESIDENT && e.path != imd::Path::kNoop;
+    r.kernel_launches = imd::plan_kernel_launches(e);
+    r.sm_count = sms_in > 0 ? sms_in : imd::kDefaultSms;
+    r.k4_config = IMD_K4_128x256;
+    if (plan_st != IMD_STATUS_SUCCESS) return plan_st;
+    r.plan_device_bytes = e.device_bytes;
+    r.plan_host_bytes = imd::plan_host_bytes(*A, *B, *C, an, e);
+    return IMD_STATUS_SUCCESS;
+  });
+  std::memcpy(out, &r, std::min<size_t>(out->struct_size, sizeof r));
+  return static_cast<imd_status_t>(r.status);
+}
+
+imd_status_t layout_impl(const imd_tensor_t* A, const imd_tensor_t* B, const imd_tensor_t* C,
+                         const imd_options_t* options, imd_region_t* regions, int32_t capacity,
+                         int32_t* num_regions, size_t* total) {
+  if (capacity < 0 || (capacity > 0 && regions == nullptr)) return IMD_STATUS_INVALID_VALUE;
+  return guarded([&]() -> imd_status_t {
+    Analysis an;
+    if (const imd_status_t st = imd::analyze(A, B, C, options, &an); st != IMD_STATUS_SUCCESS)
+      return st;
+    const int32_t n = std::min<int32_t>(capacity, IMD_REGION_COUNT);
+    for (int32_t r = 0; r < n; ++r) regions[r] = {an.layout.offset[r], an.layout.bytes[r]};
+    if (num_regions != nullptr) *num_regions = IMD_REGION_COUNT;
+    if (total != nullptr) *total = static_cast<size_t>(an.layout.total);
+    return IMD_STATUS_SUCCESS;
+  });
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t imd_host_api_version(void) { return IMD_HOST_API_VERSION; }
+
+imd_status_t imd_workspace_size(const imd_tensor_t* A, const imd_tensor_t* B,
+                                const imd_tensor_t* C, const imd_options_t* options,
+                                size_t* bytes) {
+  if (bytes == nullptr) return IMD_STATUS_INVALID_VALUE;
+  return guarded([&]() -> imd_status_t {
+    Analysis an;
+    if (const imd_status_t st = imd::analyze(A, B, C, options, &an); st != IMD_STATUS_SUCCESS)
+      return st;
+    *bytes = static_cast<size_t>(an.layout.total);
+    return IMD_STATUS_SUCCESS;
+  });
+}
+
+imd_status_t imd_workspace_layout(const imd_tensor_t* A, const imd_tensor_t* B,
+                                  const imd_tensor_t* C, const imd_options_t* options,
+                                  imd_region_t* regions, int32_t capacity, int32_t* num_regions,
+                                  size_t* total) {
+  return layout_impl(A, B, C, options, regions, capacity, num_regions, total);
+}
+
+const char* imd_region_name(int32_t region) {
+  static const char* const names[IMD_REGION_COUNT] = {"sA", "sB", "fA", "fB", "vec", "RA", "RB", "W"};
+  return region >= 0 && region < IMD_REGION_COUNT ? names[region] : nullptr;
+}
+
+imd_status_t imd_plan_bytes(const imd_tensor_t* A, const imd_tensor_t* B, const imd_tensor_t* C,
+                            const imd_options_t* options, size_t* device_bytes,
+                            size_t* host_bytes) {
+  return guarded([&]() -> imd_status_t {
+    Analysis an;
+    if (const imd_status_t st = imd::analyze(A, B, C, options, &an); st != IMD_STATUS_SUCCESS)
+      return st;
+    ExecPlan e;
+    if (const imd_status_t st = imd::make_plan(an, &e); st != IMD_STATUS_SUCCESS) return st;
+    if (device_bytes != nullptr) *device_bytes = static_cast<size_t>(e.device_bytes);
+    if (host_bytes != nullptr)
+      *host_bytes = static_cast<size_t>(imd::plan_host_bytes(*A, *B, *C, an, e));
+    return IMD_STATUS_SUCCESS;
+  });
+}
+
+imd_status_t imd_lowering(const imd_tensor_t* A, const imd_tensor_t* B, const imd_tensor_t* C,
+                          const imd_options_t* options, imd_lowering_t* out) {
+  return lowering_impl(A, B, C, options, out);
+}
+
+const char* imd_status_string(imd_status_t status) {
+  switch (status) {
+    case IMD_STATUS_SUCCESS: return "IMD_STATUS_SUCCESS";
+    case IMD_STATUS_INVALID_VALUE: return "IMD_STATUS_INVALID_VALUE";
+    case IMD_STATUS_NOT_SUPPORTED: return "IMD_STATUS_NOT_SUPPORTED";
+    case IMD_STATUS_ALIASING: return "IMD_STATUS_ALIASING";
+    case IMD_STATUS_INSUFFICIENT_WORKSPACE: return "IMD_STATUS_INSUFFICIENT_WORKSPACE";
+    case IMD_STATUS_MISALIGNED: return "IMD_STATUS_MISALIGNED";
+    case IMD_STATUS_CUDA_ERROR: return "IMD_STATUS_CUDA_ERROR";
+    case IMD_STATUS_ALLOC_FAILED: return "IMD_STATUS_ALLOC_FAILED";
+    case IMD_STATUS_PACK_MISMATCH: return "IMD_STATUS_PACK_MISMATCH";
+  }
+  return "IMD_STATUS_UNKNOWN";
+}
+
+/* ---- packed operands: queries with no packed operand behave as the in-line ones; a packed
+ *      operand is not supported yet --------------------------------------------------------- */
+imd_status_t imd_pack_layout(const imd_pack_desc_t* desc, imd_pack_layout_t* out) {
+  if (desc == nullptr || out == nullptr) return IMD_STATUS_INVALID_VALUE;
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_pack_desc_for(const imd_tensor_t*, const imd_tensor_t*, const imd_tensor_t*,
+                               const imd_options_t*, int32_t, imd_pack_desc_t*, int32_t*, int32_t) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_workspace_size_packed(const imd_tensor_t* A, const imd_tensor_t* B,
+                                       const imd_tensor_t* C, const imd_options_t* options,
+                                       const imd_packing_t* packing, size_t* bytes) {
+  const imd_status_t st = imd_workspace_size(A, B, C, options, bytes);
+  if (st != IMD_STATUS_SUCCESS) return st;
+  return any_packed(packing) ? IMD_STATUS_NOT_SUPPORTED : IMD_STATUS_SUCCESS;
+}
+imd_status_t imd_workspace_layout_packed(const imd_tensor_t* A, const imd_tensor_t* B,
+                                         const imd_tensor_t* C, const imd_options_t* options,
+                                         const imd_packing_t* packing, imd_region_t* regions,
+                                         int32_t capacity, int32_t* num_regions, size_t* total) {
+  const imd_status_t st = layout_impl(A, B, C, options, regions, capacity, num_regions, total);
+  if (st != IMD_STATUS_SUCCESS) return st;
+  return any_packed(packing) ? IMD_STATUS_NOT_SUPPORTED : IMD_STATUS_SUCCESS;
+}
+imd_status_t imd_lowering_packed(const imd_tensor_t* A, const imd_tensor_t* B,
+                                 const imd_tensor_t* C, const imd_options_t* options,
+                                 const imd_packing_t* packing, imd_lowering_t* out) {
+  if (any_packed(packing)) {
+    if (out == nullptr || out->struct_size < 136) return IMD_STATUS_INVALID_VALUE;
+    return IMD_STATUS_NOT_SUPPORTED;
+  }
+  return lowering_impl(A, B, C, options, out);
+}
+
+/* ---- performance model: not shipped for this engine yet (see the header) ------------------- */
+const char* imd_perf_kernel_name(int32_t) { return nullptr; }
+imd_status_t imd_perf_calib_default(imd_perf_calib_t*) { return IMD_STATUS_NOT_SUPPORTED; }
+imd_status_t imd_perf_calib_parse(const char*, size_t, imd_perf_calib_t*, int32_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_perf_calib_load(const char*, imd_perf_calib_t*, int32_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_perf_calib_parse_ex(const char*, size_t, imd_perf_calib_t*, imd_perf_calib_error_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_perf_calib_load_ex(const char*, imd_perf_calib_t*, imd_perf_calib_error_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_perf_calib_default_ex(imd_perf_calib_t*, imd_perf_calib_error_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+const char* imd_perf_calib_error_name(int32_t) { return nullptr; }
+imd_status_t imd_perf_calib_format(const imd_perf_calib_t*, char*, size_t, size_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+const char* imd_perf_class_name(int32_t) { return nullptr; }
+const char* imd_perf_param_name(int32_t, int32_t) { return nullptr; }
+const char* imd_perf_phase_name(int32_t) { return nullptr; }
+imd_status_t imd_perf_predict(const imd_tensor_t*, const imd_tensor_t*, const imd_tensor_t*,
+                              const imd_options_t*, const imd_packing_t*, const imd_perf_request_t*,
+                              const imd_perf_calib_t*, imd_perf_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_perf_predict_pack(const imd_pack_desc_t*, const imd_perf_request_t*,
+                                   const imd_perf_calib_t*, imd_perf_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_perf_rank(const imd_tensor_t*, const imd_tensor_t*, const imd_tensor_t*,
+                           const imd_options_t*, const imd_perf_rank_request_t*,
+                           const imd_perf_calib_t*, imd_perf_candidate_t*, int32_t, int32_t*) {
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+
+}  // extern "C"

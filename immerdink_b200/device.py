@@ -1,0 +1,350 @@
+"""Device API: plans and einsum-style contractions on caller-owned float64 CUDA arrays.
+
+Mirrors the reference front end (python/immerdink/device.py: `Plan` :511-728, `PlanCache`
+:744-809, `contract` :819-868, `workspace_size` :871-): same names, arguments, exception types
+and ownership rules. Nothing here allocates device memory, copies data or synchronises: a call
+checks the arrays' layouts on the host and enqueues imd_contract on the caller's stream, so it
+can be captured in a CUDA graph. The caller owns operands, output and workspace."""
+import ctypes as ct
+import threading
+import weakref
+from collections import namedtuple
+
+from . import _arrays, _capi, host
+from ._arrays import (DeviceArray, get_cai_stream_policy, set_cai_stream_policy,  # noqa: F401
+                      stream_handle)
+
+
+class ImmerdinkError(RuntimeError):
+    """A non-SUCCESS imd_status_t; `.status` is its name."""
+    status = "UNKNOWN"
+
+
+class InvalidValueError(ImmerdinkError, ValueError):
+    status = "INVALID_VALUE"
+
+
+class NotSupportedError(ImmerdinkError):
+    status = "NOT_SUPPORTED"
+
+
+class AliasingError(ImmerdinkError, ValueError):
+    status = "ALIASING"
+
+
+class InsufficientWorkspaceError(ImmerdinkError, ValueError):
+    status = "INSUFFICIENT_WORKSPACE"
+
+
+class MisalignedError(ImmerdinkError, ValueError):
+    status = "MISALIGNED"
+
+
+class CudaError(ImmerdinkError):
+    status = "CUDA_ERROR"
+
+
+class AllocFailedError(ImmerdinkError, MemoryError):
+    status = "ALLOC_FAILED"
+
+
+class PackMismatchError(ImmerdinkError, ValueError):
+    status = "PACK_MISMATCH"
+
+
+_BY_STATUS = {1: InvalidValueError, 2: NotSupportedError, 3: AliasingError,
+              4: InsufficientWorkspaceError, 5: MisalignedError, 6: CudaError,
+              7: AllocFailedError, 8: PackMismatchError}
+
+
+def _error(st, what, extra=""):
+    cls = _BY_STATUS.get(st, ImmerdinkError)
+    return cls(f"{what}: IMD_STATUS_{cls.status}{extra}")
+
+
+def load_library(path=None):
+    return path if isinstance(path, _capi.Library) else _capi.load(path)
+
+
+class Layout(namedtuple("Layout", "shape strides")):
+    """Extents and ELEMENT strides of an operand (None = dense), to plan before arrays exist."""
+
+    def __new__(cls, shape, strides=None):
+        shape = tuple(int(e) for e in shape)
+        strides = host.dense_strides(shape) if strides is None else tuple(int(s) for s in strides)
+        if len(strides) != len(shape):
+            raise ValueError("one stride per mode")
+        return super().__new__(cls, shape, strides)
+
+
+def _layout_of_view(v, what):
+    _, shape, bstrides, f8, _, _ = v
+    if not f8:
+        raise TypeError(f"{what}: dtype must be float64")
+    shape = tuple(int(e) for e in shape)
+    if bstrides is None:
+        return Layout(shape)
+    if any(s % 8 for s in bstrides):
+        raise TypeError(f"{what}: byte strides must be multiples of 8")
+    return Layout(shape, tuple(s // 8 for s in bstrides))
+
+
+def _layout(x, what):
+    return x if isinstance(x, Layout) else _layout_of_view(_arrays.view(x), what)
+
+
+def _descs(spec, layouts):
+    labels = host.parse_spec(spec)
+    out = []
+    for name, lab, lay in zip("ABC", labels, layouts):
+        if len(lab) != len(lay.shape):
+            raise ValueError(f"{name}: {len(lab)} labels in the spec, rank {len(lay.shape)} array")
+        out.append(host.Desc(lay.shape, lay.strides, tuple(ord(c) for c in lab)))
+    return tuple(out)
+
+
+class _Expected:
+    """Shape and strides one operand of a plan must have at call time (modes of extent <= 1
+    are free: the lowering drops them)."""
+
+    def __init__(self, desc, what):
+        self.shape, self.strides, self.what = tuple(desc.extent), tuple(desc.stride), what
+
+    def check(self, shape, bstrides):
+        shape = tuple(int(e) for e in shape)
+        if shape != self.shape:
+            raise ValueError(f"{self.what}: shape {shape} != the plan's {self.shape}")
+        if 0 in shape:
+            return
+        got = host.dense_strides(shape) if bstrides is None else tuple(s / 8 for s in bstrides)
+        if any(e > 1 and s != w for e, s, w in zip(shape, got, self.strides)):
+            raise ValueError(f"{self.what}: strides {got} (elements) != the plan's {self.strides}")
+
+
+def _pointer(x, expected, stream, out=False, device=None):
+    ptr, shape, bstrides, f8, readonly, _ = _arrays.view(x, stream, device)
+    if not f8:
+        raise TypeError(f"{expected.what}: dtype must be float64")
+    if out and readonly:
+        raise ValueError(f"{expected.what} is read-only")
+    expected.check(shape, bstrides)
+    return ptr
+
+
+class Handle:
+    """imd_create on the current device."""
+
+    def __init__(self, lib=None):
+        self.lib = load_library(lib)
+        self.device = self.lib.current_device()
+        h = ct.c_void_p()
+        st = self.lib.lib.imd_create(ct.byref(h))
+        if st:
+            raise _error(st, "imd_create")
+        self._h = h.value
+        self._fin = weakref.finalize(self, self.lib.lib.imd_destroy, h.value)
+
+    def close(self):
+        self._h = None
+        self._fin()
+
+
+_handles, _handles_lock = {}, threading.Lock()
+
+
+def default_handle(lib=None):
+    lib = load_library(lib)
+    key = (id(lib), lib.current_device())
+    with _handles_lock:
+        if key not in _handles:
+            _handles[key] = Handle(lib)
+        return _handles[key]
+
+
+class Plan:
+    """imd_plan_create for fixed operand layouts (arrays or `Layout`s). Immutable; any number
+    of threads may call `contract` at once, each with its own workspace. Footprints:
+    `workspace_bytes` (per in-flight call, caller-owned), `device_bytes` (plan-owned)."""
+
+    def __init__(self, spec, A, B, C, *, N, g=0, rounding="RN", mode="EMULATE",
+                 vec_mode="GENERATE", k4_tune=False, packs=None, handle=None, lib=None):
+        lays = [_layout(x, n) for x, n in zip((A, B, C), "ABC")]
+        self.spec = spec
+        self._create(_descs(spec, lays), N, g, rounding, mode, vec_mode, k4_tune, packs, handle, lib)
+
+    @classmethod
+    def from_descs(cls, A, B, C, *, N, g=0, rounding="RN", mode="EMULATE", vec_mode="GENERATE",
+                   k4_tune=False, packs=None, handle=None, lib=None):
+        self = cls.__new__(cls)
+        self.spec = None
+        descs = tuple(d if isinstance(d, host.Desc) else host.Desc(*d) for d in (A, B, C))
+        self._create(descs, N, g, rounding, mode, vec_mode, k4_tune, packs, handle, lib)
+        return self
+
+    def _create(self, descs, N, g, rounding, mode, vec_mode, k4_tune, packs, handle, lib):
+        if packs is not None and any(p is not None for p in packs):
+            raise NotSupportedError("packed operands are not available in this build")
+        self.lib = load_library(lib if handle is None else handle.lib)
+        self.handle = handle or default_handle(self.lib)
+        self.device = self.handle.device
+        self.descs = descs
+        self.options = dict(N=int(N), g=int(g), rounding=rounding, mode=mode, vec_mode=vec_mode,
+                            k4_tune=bool(k4_tune))
+        self._opt = host.options(N, g, rounding, mode, vec_mode, 1 if k4_tune else 0)
+        self._cd = [host.CDesc(d) for d in descs]
+        h = ct.c_void_p()
+        L = self.lib.lib
+        st = L.imd_plan_create(self.handle._h, self._cd[0].t, self._cd[1].t, self._cd[2].t,
+                               self._opt, ct.byref(h))
+        if st:
+            raise _error(st, "imd_plan_create")
+        self._h = h.value
+        self._fin = weakref.finalize(self, L.imd_plan_destroy, h.value)
+        self.workspace_bytes = host.workspace_size(descs, N=N, g=g, rounding=rounding, mode=mode,
+                                                   vec_mode=vec_mode, lib=self.lib.host)
+        nb = ct.c_size_t(0)
+        L.imd_plan_device_bytes(self._h, ct.byref(nb))
+        self.device_bytes = nb.value
+        self._ex = [_Expected(d, n) for d, n in zip(descs, "ABC")]
+        self._fn = L.imd_contract
+        self._lw = None
+
+    @property
+    def lowering(self):
+        if self._lw is None:
+            o = self.options
+            self._lw = host.lowering(self.descs, N=o["N"], g=o["g"], rounding=o["rounding"],
+                                     mode=o["mode"], vec_mode=o["vec_mode"],
+                                     sm_count=self.lib.sm_count(self.device), lib=self.lib.host)
+        return self._lw
+
+    @property
+    def host_bytes(self):
+        return self.lowering["plan_host_bytes"]
+
+    def contract(self, A, B, C, *, alpha=1.0, beta=0.0, workspace=None, stream=None, packed=None):
+        """C <- alpha A.B + beta C on `stream`. Arrays must have the plan's shapes and strides;
+        workspace >= workspace_bytes, 256-byte aligned, one in-flight call per workspace.
+        Returns C."""
+        if self._h is None:
+            raise ValueError("plan is closed")
+        if packed is not None and any(x is not None for x in packed):
+            raise ValueError("packed buffers given to a plan without packs")
+        s = 0 if stream is None else stream_handle(stream)
+        dev = self.device
+        pa = _pointer(A, self._ex[0], s, device=dev)
+        pb = _pointer(B, self._ex[1], s, device=dev)
+        pc = _pointer(C, self._ex[2], s, True, dev)
+        pw, nw = (None, 0) if workspace is None else _arrays.buffer(workspace, "workspace",
+                                                                    stream=s, device=dev)
+        st = self._fn(self._h, alpha, pa, pb, beta, pc, pw, nw, s)
+        if st:
+            raise self._fail(st, nw)
+        return C
+
+    def contract_ptr(self, alpha, A, B, beta, C, ws, ws_bytes, stream=0):
+        """imd_contract with raw integers: only the C checks."""
+        st = self._fn(self._h, alpha, A, B, beta, C, ws, ws_bytes, stream)
+        if st:
+            raise self._fail(st, ws_bytes)
+
+    def _fail(self, st, nw):
+        extra = ""
+        if st in (1, 4) and nw < self.workspace_bytes:
+            extra = f" (workspace of {nw} bytes; the plan needs {self.workspace_bytes})"
+        return _error(st, "imd_contract", extra)
+
+    def close(self):
+        self._h = None
+        if hasattr(self, "_fin"):
+            self._fin()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __repr__(self):
+        state = "closed" if self._h is None else f"workspace {self.workspace_bytes} bytes"
+        return f"<immerdink_b200.Plan {self.spec or self.descs!r} N={self.options['N']} {state}>"
+
+
+class PlanCache:
+    """Plans keyed by (spec, layouts, options, device). Thread-safe; never evicts.
+    `freeze()`: a miss raises KeyError (assert that every plan exists before a capture)."""
+
+    def __init__(self):
+        self._plans, self._lock, self.frozen = {}, threading.Lock(), False
+
+    def plans(self):
+        return list({id(p): p for p in list(self._plans.values())}.values())
+
+    def __len__(self):
+        return len(self.plans())
+
+    @property
+    def device_bytes(self):
+        return sum(p.device_bytes for p in self.plans())
+
+    def freeze(self, frozen=True):
+        self.frozen = bool(frozen)
+
+    def _get(self, key, make):
+        p = self._plans.get(key)
+        if p is None:
+            if self.frozen:
+                raise KeyError(f"PlanCache is frozen and holds no plan for {key[0]!r}")
+            new = make()
+            with self._lock:
+                p = self._plans.setdefault(key, new)
+            if p is not new:
+                new.close()
+        return p
+
+    def get(self, spec, A, B, C, *, N, g=0, rounding="RN", mode="EMULATE", vec_mode="GENERATE",
+            k4_tune=False, packs=None, lib=None):
+        lib = load_library(lib)
+        lays = tuple(_layout(x, n) for x, n in zip((A, B, C), "ABC"))
+        opts = (int(N), int(g), rounding, mode, vec_mode, bool(k4_tune))
+        key = (spec, lays, opts, id(lib), lib.current_device())
+        return self._get(key, lambda: Plan(spec, *lays, N=N, g=g, rounding=rounding, mode=mode,
+                                           vec_mode=vec_mode, k4_tune=k4_tune, packs=packs, lib=lib))
+
+    def clear(self):
+        with self._lock:
+            plans, self._plans = list(self._plans.values()), {}
+        for p in {id(p): p for p in plans}.values():
+            if p.options["vec_mode"] == "RESIDENT":
+                p.close()
+
+
+default_plan_cache = PlanCache()
+
+
+def contract(spec, A, B, out, *, alpha=1.0, beta=0.0, N, g=0, rounding="RN", mode="EMULATE",
+             vec_mode="GENERATE", k4_tune=False, workspace=None, stream=None, plan_cache=None,
+             packs=None, packed=None, lib=None):
+    """einsum-style `out <- alpha sum A B + beta out` ("ik,kj->ij") on float64 CUDA arrays.
+    The plan comes from `plan_cache` (default: the process-wide cache; False: a plan for this
+    call only). `workspace`: caller-owned, >= workspace_size(...). Returns out."""
+    lib = load_library(lib)
+    if plan_cache is False:
+        if vec_mode != "GENERATE":
+            raise ValueError("plan_cache=False needs vec_mode GENERATE")
+        with Plan(spec, A, B, out, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode,
+                  k4_tune=k4_tune, packs=packs, lib=lib) as plan:
+            return plan.contract(A, B, out, alpha=alpha, beta=beta, workspace=workspace,
+                                 stream=stream, packed=packed)
+    cache = default_plan_cache if plan_cache is None else plan_cache
+    plan = cache.get(spec, A, B, out, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode,
+                     k4_tune=k4_tune, packs=packs, lib=lib)
+    return plan.contract(A, B, out, alpha=alpha, beta=beta, workspace=workspace, stream=stream,
+                         packed=packed)
+
+
+def workspace_size(spec, A, B, C, *, N, g=0, rounding="RN", mode="EMULATE", vec_mode="GENERATE",
+                   packs=None, lib=None):
+    """Exact workspace bytes for these operands (arrays or `Layout`s); host library only."""
+    descs = _descs(spec, [_layout(x, n) for x, n in zip((A, B, C), "ABC")])
+    return host.workspace_size(descs, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode)

@@ -1,0 +1,83 @@
+/* Device-side C ABI of the B200 contraction engine: libimmerdink.so (sm_100a).
+ *
+ *   C[I,J,L] <- alpha * sum_K A[I,K,L] * B[K,J,L] + beta * C[I,J,L]     (FP64 in, FP64 out)
+ *
+ * computed by Ozaki scheme II: exact power-of-two row/column scaling, int8 residues for N
+ * coprime moduli, one int8 GEMM per modulus on tcgen05 tensor cores, exact CRT, one correctly
+ * rounded conversion. Drop-in for the reference's include/immerdink/immerdink.h: the same twelve
+ * entry points with the same argument meaning, check order and statuses; each declaration
+ * names the reference declaration it replaces as "ref: immerdink.h:<line>".
+ *
+ * Contract shared by every entry point: status codes only (nothing throws); the caller owns
+ * operands, output, workspace, packed buffers and the stream; imd_contract and imd_pack only
+ * enqueue kernels (no allocation, no synchronisation, no write to the plan). */
+#ifndef IMMERDINK_B200_H
+#define IMMERDINK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include <cuda_runtime_api.h>
+
+#include "immerdink/immerdink_host.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct imd_handle_st* imd_handle_t;
+typedef struct imd_plan_st* imd_plan_t;
+typedef struct imd_pack_s* imd_pack_t;
+
+/* Library context, bound to the current device. ref: immerdink.h:28-29 */
+IMD_API imd_status_t imd_create(imd_handle_t* handle);
+IMD_API imd_status_t imd_destroy(imd_handle_t handle);
+
+/* Lower the contraction, check legality and RN acceptance, and precompute everything the
+ * kernels are launched with (including the function attributes of the tcgen05 GEMM and the
+ * driver entry point used to encode TMA descriptors), so that imd_contract touches no global
+ * state. With IMD_VEC_RESIDENT the plan owns device scatter vectors. ref: immerdink.h:35-38 */
+IMD_API imd_status_t imd_plan_create(imd_handle_t handle, const imd_tensor_t* A,
+                                     const imd_tensor_t* B, const imd_tensor_t* C,
+                                     const imd_options_t* options, imd_plan_t* plan);
+IMD_API imd_status_t imd_plan_destroy(imd_plan_t plan);
+
+/* Device bytes owned by the plan (= imd_plan_bytes). ref: immerdink.h:43 */
+IMD_API imd_status_t imd_plan_device_bytes(imd_plan_t plan, size_t* bytes);
+
+/* Enqueue one contraction on `stream`. Checks, in order: null pointers (C always; A, B unless
+ * alpha == 0 or k == 0; ws when the plan needs one) -> INVALID_VALUE; empty output -> SUCCESS;
+ * ALIASING (byte intervals C/A, C/B, ws/A, ws/B, ws/C); MISALIGNED (8 bytes, ws 256);
+ * ws_bytes < imd_workspace_size -> INSUFFICIENT_WORKSPACE. A failing call touches nothing.
+ * One workspace serves one in-flight call. ref: immerdink.h:49-51 */
+IMD_API imd_status_t imd_contract(imd_plan_t plan, double alpha, const double* A,
+                                  const double* B, double beta, double* C, void* ws,
+                                  size_t ws_bytes, cudaStream_t stream);
+
+/* Packed operands: one operand scaled and reduced to all N residue planes once, reused by many
+ * contractions. ref: immerdink.h:64-82, 89-92, 95-102, 119-121 */
+IMD_API imd_status_t imd_pack_create(imd_handle_t handle, const imd_pack_desc_t* desc,
+                                     imd_pack_t* pack);
+IMD_API imd_status_t imd_pack_destroy(imd_pack_t pack);
+IMD_API imd_status_t imd_pack_bytes(imd_pack_t pack, size_t* pack_bytes, size_t* pack_ws_bytes);
+IMD_API imd_status_t imd_pack(imd_pack_t pack, const double* X, void* packed,
+                              size_t packed_bytes, void* ws, size_t ws_bytes,
+                              cudaStream_t stream);
+IMD_API imd_status_t imd_plan_create_packed(imd_handle_t handle, const imd_tensor_t* A,
+                                            const imd_tensor_t* B, const imd_tensor_t* C,
+                                            const imd_options_t* options, imd_pack_t packA,
+                                            imd_pack_t packB, imd_plan_t* plan);
+typedef struct {
+  const double* data;  /* the FP64 operand (native path of flagged outputs, DIRECT, in-line) */
+  const void* packed;  /* imd_pack's output for a packed slot, else NULL */
+  size_t packed_bytes;
+  imd_pack_t pack;     /* packed slot: a handle with the plan's key; in-line slot: NULL */
+} imd_operand_t;
+IMD_API imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operand_t* A,
+                                         const imd_operand_t* B, double beta, double* C,
+                                         void* ws, size_t ws_bytes, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IMMERDINK_B200_H */
