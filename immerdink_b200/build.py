@@ -70,7 +70,7 @@ def build_cuda(force=False, verbose=False):
     cmd = [_nvcc(), "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
            "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-ccbin", _cxx(),
            "-I" + INCLUDE, "-I" + CSRC, *CUDA_SOURCES, "-o", CUDA_LIB,
-           "-L" + HERE, "-limmerdink_host", "-Xlinker", "-rpath=$ORIGIN", "-lcudart"]
+           "-L" + HERE, "-limmerdink_host", "-Xlinker", "-rpath=$ORIGIN"]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

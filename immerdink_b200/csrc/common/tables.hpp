@@ -37,6 +37,41 @@ struct CrtTables {
   uint32_t H[kCrtLimbs];               // P / 2 - 1: the largest representable |z|
 };
 
+// Constants of the residue emitter for one N (uniform across a warp: kernels take them by value
+// and read them from the constant bank).
+struct ResidueTables {
+  int32_t N;
+  int32_t words;                         // 32-bit words of |a'|: 2 (N <= 16) or 3
+  uint32_t p[kMaxModuli];
+  uint32_t half[kMaxModuli];             // floor(p / 2)
+  uint32_t magic[kMaxModuli];            // ceil(2^32 / p)
+  uint32_t lift[kMaxModuli];             // a multiple of p >= 2^20: makes negated sums nonnegative
+  uint32_t weight[3][kMaxModuli];        // 4 packed byte weights 2^(8 (4 j + i)) mod p
+};
+
+inline ResidueTables residue_tables(int N) {
+  ResidueTables t{};
+  t.N = N;
+  t.words = N <= 16 ? 2 : 3;
+  for (int l = 0; l < N; ++l) {
+    const uint32_t p = static_cast<uint32_t>(kModuli[l]);
+    t.p[l] = p;
+    t.half[l] = p / 2;
+    t.magic[l] = static_cast<uint32_t>(((uint64_t{1} << 32) + p - 1) / p);
+    t.lift[l] = ((1u << 20) + p - 1) / p * p;
+    uint32_t pw = 1 % p;
+    for (int j = 0; j < 3; ++j) {
+      uint32_t word = 0;
+      for (int i = 0; i < 4; ++i) {
+        word |= pw << (8 * i);
+        pw = (pw * 256u) % p;
+      }
+      t.weight[j][l] = word;
+    }
+  }
+  return t;
+}
+
 struct PlanConstants {
   Big P, H, T;
 };

@@ -1,0 +1,219 @@
+// C ABI of libimmerdink.so. Argument checks follow the order the reference documents and
+// implements (src/api.cpp:293-334 for imd_contract, :120-199 for plan creation): a failing call
+// touches nothing. No exception leaves a function. All sizing and legality come from
+// libimmerdink_host (host/plan.hpp); this file adds the device-side parts of a plan.
+#include <cstdint>
+#include <memory>
+#include <new>
+
+#include <cuda_runtime_api.h>
+
+#include "immerdink/immerdink.h"
+#include "kernels.hpp"
+
+struct imd_handle_st {
+  int device = 0;
+};
+struct imd_pack_s {
+  int unused = 0;
+};
+
+namespace {
+
+using i128 = __int128;
+
+bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Bytes a strided FP64 view can address, [lo, hi); empty for a null pointer or an empty tensor.
+struct Interval {
+  i128 lo = 0, hi = 0;
+};
+Interval tensor_bytes(const imd::TensorCopy& t, const void* p) {
+  Interval r;
+  if (p == nullptr) return r;
+  i128 below = 0, above = 0;
+  for (size_t d = 0; d < t.extent.size(); ++d) {
+    if (t.extent[d] == 0) return r;
+    const i128 span = static_cast<i128>(t.stride[d]) * (t.extent[d] - 1);
+    (span < 0 ? below : above) += span;
+  }
+  const i128 base = static_cast<i128>(reinterpret_cast<uintptr_t>(p));
+  r.lo = base + 8 * below;
+  r.hi = base + 8 * above + 8;
+  return r;
+}
+Interval raw_bytes(const void* p, uint64_t n) {
+  Interval r;
+  if (p == nullptr || n == 0) return r;
+  r.lo = static_cast<i128>(reinterpret_cast<uintptr_t>(p));
+  r.hi = r.lo + static_cast<i128>(n);
+  return r;
+}
+bool overlap(const Interval& x, const Interval& y) {
+  return x.lo < x.hi && y.lo < y.hi && x.lo < y.hi && y.lo < x.hi;
+}
+
+}  // namespace
+
+extern "C" {
+
+imd_status_t imd_create(imd_handle_t* handle) {
+  if (handle == nullptr) return IMD_STATUS_INVALID_VALUE;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
+  auto* h = new (std::nothrow) imd_handle_st{device};
+  if (h == nullptr) return IMD_STATUS_ALLOC_FAILED;
+  *handle = h;
+  return IMD_STATUS_SUCCESS;
+}
+
+imd_status_t imd_destroy(imd_handle_t handle) {
+  delete handle;
+  return IMD_STATUS_SUCCESS;
+}
+
+imd_status_t imd_plan_create(imd_handle_t handle, const imd_tensor_t* A, const imd_tensor_t* B,
+                             const imd_tensor_t* C, const imd_options_t* options,
+                             imd_plan_t* plan) {
+  if (handle == nullptr || plan == nullptr) return IMD_STATUS_INVALID_VALUE;
+  try {
+    imd::Analysis an;
+    if (const imd_status_t st = imd::analyze(A, B, C, options, &an); st != IMD_STATUS_SUCCESS)
+      return st;
+    imd::ExecPlan e;
+    if (const imd_status_t st = imd::make_plan(an, &e); st != IMD_STATUS_SUCCESS) return st;
+    auto p = std::make_unique<imd_plan_st>();
+    p->options = an.options;
+    p->view = an.view;
+    p->A = imd::TensorCopy(*A), p->B = imd::TensorCopy(*B), p->C = imd::TensorCopy(*C);
+    p->exec = e;
+    p->crt = imd::crt_tables(e.N);
+    p->res = imd::residue_tables(e.N);
+    if (e.path != imd::Path::kNoop) {
+      if (cudaGetDevice(&p->device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&p->sms, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess) {
+        cudaGetLastError();
+        return IMD_STATUS_CUDA_ERROR;
+      }
+    }
+    if (e.emulated()) {
+      imd::GemmPlanInfo info;
+      if (const imd_status_t st = imd::gemm_setup(&info); st != IMD_STATUS_SUCCESS) return st;
+      p->encode_tiled = info.encode_tiled;
+      p->error_word = info.error_word;
+    }
+    if (e.vec_resident) {
+      void* dev = nullptr;
+      const cudaError_t err = cudaMalloc(&dev, static_cast<size_t>(e.device_bytes));
+      if (err != cudaSuccess) {
+        cudaGetLastError();
+        return err == cudaErrorMemoryAllocation ? IMD_STATUS_ALLOC_FAILED : IMD_STATUS_CUDA_ERROR;
+      }
+      p->vec_dev = dev;
+      if (imd::generate_vectors(e, static_cast<int64_t*>(dev), cudaStreamPerThread) !=
+              IMD_STATUS_SUCCESS ||
+          cudaStreamSynchronize(cudaStreamPerThread) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(dev);
+        return IMD_STATUS_CUDA_ERROR;
+      }
+    }
+    *plan = p.release();
+    return IMD_STATUS_SUCCESS;
+  } catch (const std::bad_alloc&) {
+    return IMD_STATUS_ALLOC_FAILED;
+  } catch (...) {
+    return IMD_STATUS_INVALID_VALUE;
+  }
+}
+
+imd_status_t imd_plan_destroy(imd_plan_t plan) {
+  if (plan != nullptr && plan->vec_dev != nullptr) cudaFree(plan->vec_dev);
+  delete plan;
+  return IMD_STATUS_SUCCESS;
+}
+
+imd_status_t imd_plan_device_bytes(imd_plan_t plan, size_t* bytes) {
+  if (plan == nullptr || bytes == nullptr) return IMD_STATUS_INVALID_VALUE;
+  *bytes = plan->exec.vec_resident ? static_cast<size_t>(plan->exec.device_bytes) : 0;
+  return IMD_STATUS_SUCCESS;
+}
+
+imd_status_t imd_contract(imd_plan_t plan, double alpha, const double* A, const double* B,
+                          double beta, double* C, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (plan == nullptr) return IMD_STATUS_INVALID_VALUE;
+  if (!plan->slot_key[0].empty() || !plan->slot_key[1].empty()) return IMD_STATUS_PACK_MISMATCH;
+  const imd::ExecPlan& e = plan->exec;
+  const bool reads_ab = alpha != 0.0 && e.k != 0;
+  const uint64_t need = e.layout.total;
+  if (C == nullptr || (reads_ab && (A == nullptr || B == nullptr)) || (need > 0 && ws == nullptr))
+    return IMD_STATUS_INVALID_VALUE;
+  if (e.path == imd::Path::kNoop) return IMD_STATUS_SUCCESS;
+  const Interval iA = tensor_bytes(plan->A, A), iB = tensor_bytes(plan->B, B),
+                 iC = tensor_bytes(plan->C, C), iW = raw_bytes(ws, need);
+  if (overlap(iC, iA) || overlap(iC, iB) || overlap(iW, iA) || overlap(iW, iB) || overlap(iW, iC))
+    return IMD_STATUS_ALIASING;
+  if (!aligned(A, 8) || !aligned(B, 8) || !aligned(C, 8) || (need > 0 && !aligned(ws, imd::kRegionAlign)))
+    return IMD_STATUS_MISALIGNED;
+  if (ws_bytes < need) return IMD_STATUS_INSUFFICIENT_WORKSPACE;
+  const double* gA = e.swapped ? B : A;
+  const double* gB = e.swapped ? A : B;
+  try {
+    return imd::enqueue_contract(*plan, alpha, gA, gB, beta, C, ws, stream);
+  } catch (...) {
+    return IMD_STATUS_CUDA_ERROR;
+  }
+}
+
+/* ---- packed operands: not available yet; the entry points exist and refuse ----------------- */
+imd_status_t imd_pack_create(imd_handle_t handle, const imd_pack_desc_t* desc, imd_pack_t* pack) {
+  if (handle == nullptr || desc == nullptr || pack == nullptr) return IMD_STATUS_INVALID_VALUE;
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_pack_destroy(imd_pack_t pack) {
+  delete pack;
+  return IMD_STATUS_SUCCESS;
+}
+imd_status_t imd_pack_bytes(imd_pack_t pack, size_t*, size_t*) {
+  return pack == nullptr ? IMD_STATUS_INVALID_VALUE : IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_pack(imd_pack_t pack, const double*, void*, size_t, void*, size_t, cudaStream_t) {
+  return pack == nullptr ? IMD_STATUS_INVALID_VALUE : IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_plan_create_packed(imd_handle_t handle, const imd_tensor_t* A,
+                                    const imd_tensor_t* B, const imd_tensor_t* C,
+                                    const imd_options_t* options, imd_pack_t packA,
+                                    imd_pack_t packB, imd_plan_t* plan) {
+  if (packA == nullptr && packB == nullptr) return imd_plan_create(handle, A, B, C, options, plan);
+  return IMD_STATUS_NOT_SUPPORTED;
+}
+imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operand_t* A,
+                                 const imd_operand_t* B, double beta, double* C, void* ws,
+                                 size_t ws_bytes, cudaStream_t stream) {
+  if (plan == nullptr || A == nullptr || B == nullptr) return IMD_STATUS_INVALID_VALUE;
+  if (A->packed != nullptr || A->pack != nullptr || B->packed != nullptr || B->pack != nullptr)
+    return IMD_STATUS_PACK_MISMATCH;
+  return imd_contract(plan, alpha, A->data, B->data, beta, C, ws, ws_bytes, stream);
+}
+
+/* ---- verification hooks (not part of the drop-in ABI) ---------------------------------------- */
+/* 1: run the slow exact int8 GEMM instead of the tensor-core kernel in later calls (cross-check). */
+IMD_API int imd_test_use_reference_gemm(int on) {
+  imd::use_reference_gemm() = on != 0;
+  return 0;
+}
+/* Reads (and clears) the sticky device error word: nonzero when a bounded wait in a kernel gave
+ * up. Synchronises the device. */
+IMD_API unsigned int imd_test_device_error(void) {
+  unsigned int v = 0, zero = 0;
+  unsigned int* p = imd::device_error_word();
+  if (p == nullptr || cudaDeviceSynchronize() != cudaSuccess) return 0xFFFFFFFFu;
+  cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost);
+  cudaMemcpy(p, &zero, sizeof zero, cudaMemcpyHostToDevice);
+  return v;
+}
+
+}  // extern "C"

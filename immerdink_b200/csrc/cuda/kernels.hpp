@@ -1,0 +1,56 @@
+// Declarations shared by the C ABI (api.cpp), the pipeline (pipeline.cu) and the tcgen05 GEMM
+// (gemm_tcgen05.cu). Everything a kernel needs is passed by value in its parameters, so a plan
+// may be destroyed as soon as imd_contract has returned and a captured graph replays without it.
+#pragma once
+#include <cstdint>
+
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include "common/tables.hpp"
+#include "host/plan.hpp"
+#include "immerdink/immerdink.h"
+
+namespace imd {
+
+// One GEMM launch: planes [plane0, plane0 + planes) of the residue buffers, K range
+// [k0, k0 + klen) of every row, into W planes starting at modulus mod0.
+struct GemmShape {
+  int32_t m, n_hat;        // rows of A per plane; padded rows of B per plane (= W row pitch)
+  int32_t k_hat;           // row pitch of the residue planes (bytes)
+  int32_t k0, klen;        // K chunk
+  int32_t planes;          // slots x batches in this launch
+  int32_t batches;         // b
+  int32_t mod0;            // first modulus of the group
+  int32_t add;             // 0: W = acc mod p; 1: W = (W + acc) mod p
+  uint32_t p[kMaxModuli];      // moduli of the group's slots (index = slot)
+  uint32_t magic[kMaxModuli];  // floor(2^32 / p)
+  uint32_t bias[kMaxModuli];   // the multiple of p in [2^31, 2^31 + p)
+};
+
+struct GemmPlanInfo {
+  void* encode_tiled = nullptr;
+  unsigned int* error_word = nullptr;
+  int sms = 0;
+};
+
+imd_status_t gemm_setup(GemmPlanInfo* info);   // plan time: function attributes, driver entry point
+imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int8_t* RA,
+                         const int8_t* RB, uint8_t* W, cudaStream_t stream);
+// Slow exact int8 GEMM with the same contract: a second, independent implementation used only
+// by the verification hooks to cross-check the tensor-core kernel at sizes a CPU cannot reach.
+imd_status_t gemm_reference_launch(const GemmShape& s, const int8_t* RA, const int8_t* RB,
+                                   uint8_t* W, cudaStream_t stream);
+
+imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
+                              const double* B, double beta, double* C, void* ws,
+                              cudaStream_t stream);
+imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stream);
+
+// Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.
+bool& use_reference_gemm();
+
+// Sticky device-side error word (bounded waits that gave up); read by the verification hook.
+unsigned int* device_error_word();
+
+}  // namespace imd

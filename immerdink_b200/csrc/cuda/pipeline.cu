@@ -1,0 +1,533 @@
+// The kernel sequence of one imd_contract on the caller's stream (enqueue only: no allocation,
+// no synchronisation, no global state written):
+//
+//   vectors   nine int64 scatter vectors from the fused-mode table      (unless plan-resident)
+//   scale     per row of A / column of B: non-finite flag, exponent, exact sum of squares,
+//             shift sigma                                                     (one launch each)
+//   residues  gather FP64 through the vectors, quantise with sigma, reduce to the int8 residues
+//             of one group of moduli, K-contiguous planes                     (per group, each)
+//   gemm      int8 GEMM per modulus on tcgen05 tensor cores with a mod-p epilogue into u8 planes
+//   crt       exact CRT over the N planes, one rounding, alpha / beta, scatter into C
+//
+// plus the two degenerate paths: C <- beta C (alpha = 0 or k = 0) and the native FP64 FMA dot
+// (DIRECT mode or k = 1). The sequence replaces the reference's enqueue_contract
+// (src/contract.cu:1334-1485) and its kernels K0, K1, K2/K3, KF, KL, K5, k_direct,
+// k5_beta_only; the numerics are in numerics.cuh.
+#include <cstdint>
+
+#include "kernels.hpp"
+#include "numerics.cuh"
+
+namespace imd {
+
+namespace {
+
+__device__ unsigned int g_error_word = 0;
+
+constexpr int kThreads = 256;
+
+// ---- scatter vectors -------------------------------------------------------------------------
+struct VecParams {
+  ModeTable modes;
+  int64_t m, n, k, b;
+};
+
+__device__ __forceinline__ int64_t radix_offset(const ModeTable& t, int cls, int X, int64_t q) {
+  int64_t off = 0;
+  const int first = t.first[cls], cnt = t.count[cls];
+  for (int i = 0; i < cnt; ++i) {
+    const int64_t e = t.extent[first + i];
+    const int64_t d = q % e;
+    q /= e;
+    off += d * t.stride[first + i][X];
+  }
+  return off;
+}
+
+__global__ void __launch_bounds__(kThreads) k_vectors(const __grid_constant__ VecParams p,
+                                                      int64_t* __restrict__ vec) {
+  const int64_t total = 2 * p.m + 2 * p.n + 2 * p.k + 3 * p.b;
+  const int64_t seg[9] = {p.m, p.k, p.b, p.k, p.n, p.b, p.m, p.n, p.b};
+  const int cls[9] = {kClsI, kClsK, kClsL, kClsK, kClsJ, kClsL, kClsI, kClsJ, kClsL};
+  const int ten[9] = {kTenA, kTenA, kTenA, kTenB, kTenB, kTenB, kTenC, kTenC, kTenC};
+  for (int64_t e = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; e < total;
+       e += static_cast<int64_t>(gridDim.x) * kThreads) {
+    int64_t q = e;
+    int s = 0;
+    while (s < 8 && q >= seg[s]) {
+      q -= seg[s];
+      ++s;
+    }
+    vec[e] = radix_offset(p.modes, cls[s], ten[s], q);
+  }
+}
+
+struct Vectors {
+  const int64_t *a_row, *a_k, *a_bat, *b_k, *b_col, *b_bat, *c_row, *c_col, *c_bat;
+};
+
+Vectors split_vectors(const int64_t* v, const ExecPlan& e) {
+  Vectors r;
+  r.a_row = v, v += e.m;
+  r.a_k = v, v += e.k;
+  r.a_bat = v, v += e.b;
+  r.b_k = v, v += e.k;
+  r.b_col = v, v += e.n;
+  r.b_bat = v, v += e.b;
+  r.c_row = v, v += e.m;
+  r.c_col = v, v += e.n;
+  r.c_bat = v;
+  return r;
+}
+
+// ---- scale -----------------------------------------------------------------------------------
+// A CTA owns 2^lg_rt rows completely (a row's shift is produced and consumed inside one CTA);
+// its 256 threads are 2^lg_rt rows x KT lanes along K. `rows_fast` picks which of the two runs
+// along consecutive threads, so that global loads coalesce along the operand's fast direction.
+struct ScaleParams {
+  const double* X;
+  const int64_t *row, *kv, *bat;
+  int64_t rows, batches, k;
+  int32_t lg_rt;
+  int32_t rows_fast;
+  int32_t lhs_shift;
+  Wide<8> rhs;
+  int16_t* sigma;
+  uint8_t* flag;
+};
+
+__global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ ScaleParams p) {
+  __shared__ int s_gamma[kThreads];
+  __shared__ uint64_t s_hi[kThreads], s_lo[kThreads];
+  const int RT = 1 << p.lg_rt, KT = kThreads >> p.lg_rt;
+  const int tid = threadIdx.x;
+  const int r = p.rows_fast ? (tid & (RT - 1)) : (tid / KT);
+  const int kl = p.rows_fast ? (tid >> p.lg_rt) : (tid % KT);
+  const int64_t total = p.rows * p.batches;
+  const int64_t rho = static_cast<int64_t>(blockIdx.x) * RT + r;
+  const bool live = rho < total;
+  const double* base = p.X;
+  if (live) base += p.bat[rho / p.rows] + p.row[rho % p.rows];
+
+  // pass 1: non-finite flag and largest exponent. Encoding: bit 30 = flag; low bits = gamma + 2048
+  // (0 = no finite nonzero entry).
+  int g = 0;
+  if (live)
+    for (int64_t h = kl; h < p.k; h += KT) {
+      const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h]]));
+      uint64_t M;
+      int E;
+      const int c = dev::decompose(u, &M, &E);
+      if (c < 0) g |= 1 << 30;
+      else if (c > 0) g = (g & (1 << 30)) | max(g & 0xFFFF, E + 52 + 2048);
+    }
+  const int slot = r * KT + kl;
+  s_gamma[slot] = g;
+  __syncthreads();
+  for (int s = KT >> 1; s > 0; s >>= 1) {
+    if (kl < s) {
+      const int a = s_gamma[slot], b = s_gamma[slot + s];
+      s_gamma[slot] = ((a | b) & (1 << 30)) | max(a & 0xFFFF, b & 0xFFFF);
+    }
+    __syncthreads();
+  }
+  const int gf = s_gamma[r * KT];
+  const bool any = (gf & 0xFFFF) != 0;
+  const int gamma = (gf & 0xFFFF) - 2048;
+
+  // pass 2: S = sum ceil(x^2 2^60), exact in 128 bits, order-independent
+  uint64_t hi = 0, lo = 0;
+  if (live && any)
+    for (int64_t h = kl; h < p.k; h += KT) {
+      const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h]]));
+      uint64_t M;
+      int E;
+      if (dev::decompose(u, &M, &E) == 1) {
+        uint64_t th, tl;
+        dev::square_term(M, E, gamma, &th, &tl);
+        lo += tl;
+        hi += th + (lo < tl ? 1 : 0);
+      }
+    }
+  s_hi[slot] = hi;
+  s_lo[slot] = lo;
+  __syncthreads();
+  for (int s = KT >> 1; s > 0; s >>= 1) {
+    if (kl < s) {
+      const uint64_t bl = s_lo[slot + s];
+      const uint64_t nl = s_lo[slot] + bl;
+      s_hi[slot] += s_hi[slot + s] + (nl < bl ? 1 : 0);
+      s_lo[slot] = nl;
+    }
+    __syncthreads();
+  }
+  if (live && kl == 0) {
+    int sg = 0;
+    if (any) sg = dev::shift_from_sum(s_hi[slot], s_lo[slot], p.lhs_shift, p.rhs, gamma);
+    p.sigma[rho] = static_cast<int16_t>(sg);
+    p.flag[rho] = (gf >> 30) & 1;
+  }
+}
+
+// ---- residues --------------------------------------------------------------------------------
+// One thread = 16 consecutive K positions of one row: gather, quantise, emit the group's moduli as
+// 16-byte stores into K-contiguous int8 planes R[slot][batch][rows_pad][k_hat]. Rows >= rows (the
+// padding up to rows_pad) and positions >= k (the padding up to k_hat) are written as zeros, so
+// every byte the GEMM reads is written by this call.
+struct ResidueParams {
+  const double* X;
+  const int64_t *row, *kv, *bat;
+  int64_t rows, rows_pad, batches, k, k_hat;
+  int32_t rows_fast;
+  int32_t trunc;
+  int32_t mod0, mods;  // first modulus and number of moduli of the group
+  const int16_t* sigma;
+  int8_t* R;
+  ResidueTables t;
+};
+
+template <int WORDS>
+__global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ ResidueParams p) {
+  const int64_t chunks = p.k_hat >> 4;
+  const int64_t total_rows = p.rows_pad * p.batches;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (item >= total_rows * chunks) return;
+  int64_t rho, c;
+  if (p.rows_fast) {
+    rho = item % total_rows;
+    c = item / total_rows;
+  } else {
+    c = item % chunks;
+    rho = item / chunks;
+  }
+  const int64_t lam = rho / p.rows_pad, i = rho % p.rows_pad;
+  const bool live = i < p.rows;
+  uint32_t w0[16], w1[16], w2[16];
+  uint32_t negmask = 0;
+  const int64_t h0 = c << 4;
+  if (live) {
+    const double* base = p.X + p.bat[lam] + p.row[i];
+    const int sg = p.sigma[lam * p.rows + i];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      uint64_t lo = 0;
+      uint32_t hi = 0;
+      bool neg = false;
+      if (h0 + e < p.k) {
+        const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h0 + e]]));
+        dev::quantize(u, sg, p.trunc != 0, &lo, &hi, &neg);
+      }
+      w0[e] = static_cast<uint32_t>(lo);
+      w1[e] = static_cast<uint32_t>(lo >> 32);
+      w2[e] = hi;
+      negmask |= (neg ? 1u : 0u) << e;
+    }
+  }
+  int8_t* out = p.R + (lam * p.rows_pad + i) * p.k_hat + h0;
+  const int64_t plane = p.batches * p.rows_pad * p.k_hat;
+  for (int s = 0; s < p.mods; ++s) {
+    uint32_t pk[4] = {0, 0, 0, 0};
+    if (live) {
+      const int l = p.mod0 + s;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int r = dev::residue<WORDS>(p.t, l, w0[e], w1[e], w2[e], (negmask >> e) & 1);
+        pk[e >> 2] |= (static_cast<uint32_t>(r) & 0xFFu) << (8 * (e & 3));
+      }
+    }
+    *reinterpret_cast<uint4*>(out + s * plane) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+}
+
+// ---- CRT + output ------------------------------------------------------------------------------
+struct CrtParams {
+  const uint8_t* W;            // [N][b][m][n_hat]
+  const int16_t *sigma, *tau;  // [b][m], [b][n]
+  const uint8_t *fA, *fB;
+  const double *A, *B;         // post-swap operands (native path of flagged outputs)
+  double* C;
+  Vectors v;
+  int64_t m, n, n_hat, k, b;
+  double alpha, beta;
+  CrtTables t;
+};
+
+__device__ __forceinline__ double finish(double D, double alpha, double beta, const double* c) {
+  const double E = (alpha == 1.0) ? D : __dmul_rn(alpha, D);
+  return (beta == 0.0) ? E : __fma_rn(beta, *c, E);
+}
+
+__device__ __noinline__ double native_dot(const double* a, const double* b, const int64_t* ak,
+                                          const int64_t* bk, int64_t k) {
+  double acc = 0.0;
+  for (int64_t h = 0; h < k; ++h) acc = __fma_rn(a[ak[h]], b[bk[h]], acc);
+  return acc;
+}
+
+// One thread = 4 consecutive columns of one row of one batch.
+template <int LIMBS>
+__global__ void __launch_bounds__(kThreads) k_crt(const __grid_constant__ CrtParams p) {
+  const int64_t quads = p.n_hat >> 2;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (item >= p.b * p.m * quads) return;
+  const int64_t jq = item % quads, rho = item / quads;
+  const int64_t lam = rho / p.m, i = rho % p.m;
+  const int64_t j0 = jq << 2;
+  if (j0 >= p.n) return;
+  const int64_t plane = p.b * p.m * p.n_hat;
+  const uint8_t* w = p.W + (lam * p.m + i) * p.n_hat + j0;
+  uint32_t packed[kMaxModuli];
+#pragma unroll
+  for (int l = 0; l < kMaxModuli; ++l)
+    packed[l] = l < p.t.N ? *reinterpret_cast<const uint32_t*>(w + l * plane) : 0u;
+  const int si = p.sigma[lam * p.m + i];
+  const bool fa = p.fA[lam * p.m + i] != 0;
+  double* crow = p.C + p.v.c_bat[lam] + p.v.c_row[i];
+#pragma unroll 1
+  for (int e = 0; e < 4; ++e) {
+    const int64_t j = j0 + e;
+    if (j >= p.n) break;
+    double D;
+    if (fa || p.fB[lam * p.n + j] != 0) {
+      D = native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j],
+                     p.v.a_k, p.v.b_k, p.k);
+    } else {
+      uint32_t mag[LIMBS];
+      bool neg;
+      dev::crt<LIMBS>(p.t, packed, e, mag, &neg);
+      D = dev::round_scaled<LIMBS>(mag, neg, -(si + static_cast<int>(p.tau[lam * p.n + j])));
+    }
+    double* c = crow + p.v.c_col[j];
+    *c = finish(D, p.alpha, p.beta, c);
+  }
+}
+
+// ---- degenerate paths --------------------------------------------------------------------------
+struct EpilogueOnlyParams {
+  const double *A, *B;
+  double* C;
+  Vectors v;
+  int64_t m, n, k, b;
+  double alpha, beta;
+};
+
+__global__ void __launch_bounds__(kThreads) k_direct(const __grid_constant__ EpilogueOnlyParams p) {
+  const int64_t total = p.b * p.m * p.n;
+  for (int64_t e = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; e < total;
+       e += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t j = e % p.n, i = (e / p.n) % p.m, lam = e / (p.n * p.m);
+    const double D = native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i],
+                                p.B + p.v.b_bat[lam] + p.v.b_col[j], p.v.a_k, p.v.b_k, p.k);
+    double* c = p.C + p.v.c_bat[lam] + p.v.c_row[i] + p.v.c_col[j];
+    *c = finish(D, p.alpha, p.beta, c);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) k_beta(const __grid_constant__ EpilogueOnlyParams p) {
+  const int64_t total = p.b * p.m * p.n;
+  for (int64_t e = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; e < total;
+       e += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t j = e % p.n, i = (e / p.n) % p.m, lam = e / (p.n * p.m);
+    double* c = p.C + p.v.c_bat[lam] + p.v.c_row[i] + p.v.c_col[j];
+    *c = (p.beta == 0.0) ? 0.0 : __dmul_rn(p.beta, *c);
+  }
+}
+
+// ---- reference int8 GEMM (verification only) ----------------------------------------------------
+__global__ void __launch_bounds__(kThreads) k_gemm_reference(const __grid_constant__ GemmShape s,
+                                                             const int8_t* __restrict__ RA,
+                                                             const int8_t* __restrict__ RB,
+                                                             uint8_t* __restrict__ W) {
+  const int64_t per_plane = static_cast<int64_t>(s.m) * s.n_hat;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (item >= per_plane * s.planes) return;
+  const int64_t z = item / per_plane, rem = item % per_plane;
+  const int64_t i = rem / s.n_hat, j = rem % s.n_hat;
+  const int slot = static_cast<int>(z / s.batches);
+  const int8_t* a = RA + (z * s.m + i) * static_cast<int64_t>(s.k_hat) + s.k0;
+  const int8_t* b = RB + (z * s.n_hat + j) * static_cast<int64_t>(s.k_hat) + s.k0;
+  int acc = 0;
+  for (int h = 0; h < s.klen; h += 4)
+    acc = __dp4a(*reinterpret_cast<const int*>(a + h), *reinterpret_cast<const int*>(b + h), acc);
+  uint8_t* w = W + ((static_cast<int64_t>(s.mod0 + slot) * s.batches + z % s.batches) * s.m + i) * s.n_hat + j;
+  const int64_t v = static_cast<int64_t>(acc) + (s.add ? *w : 0);
+  const int64_t pm = s.p[slot];
+  int64_t r = v % pm;
+  if (r < 0) r += pm;
+  *w = static_cast<uint8_t>(r);
+}
+
+unsigned int grid_for(int64_t items, int64_t cap = int64_t{1} << 30) {
+  int64_t g = (items + kThreads - 1) / kThreads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return static_cast<unsigned int>(g);
+}
+
+bool launched() { return cudaPeekAtLastError() == cudaSuccess; }
+
+int scale_lg_rt(bool rows_fast, int64_t k) {
+  if (rows_fast) return 5;  // 32 rows x 8 K lanes
+  int lanes = 1;
+  while (lanes < 256 && lanes < k) lanes <<= 1;
+  int lg = 0;
+  while ((256 >> lg) > lanes) ++lg;
+  return lg;
+}
+
+}  // namespace
+
+unsigned int* device_error_word() {
+  unsigned int* p = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_error_word);
+  return p;
+}
+
+imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stream) {
+  VecParams p;
+  p.modes = e.modes;
+  p.m = e.m, p.n = e.n, p.k = e.k, p.b = e.b;
+  k_vectors<<<grid_for(e.vec_count, 1 << 20), kThreads, 0, stream>>>(p, vec);
+  return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+imd_status_t gemm_reference_launch(const GemmShape& s, const int8_t* RA, const int8_t* RB,
+                                   uint8_t* W, cudaStream_t stream) {
+  const int64_t items = static_cast<int64_t>(s.m) * s.n_hat * s.planes;
+  k_gemm_reference<<<grid_for(items), kThreads, 0, stream>>>(s, RA, RB, W);
+  return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+GemmShape gemm_shape(const ExecPlan& e, int mod0, int mods, int chunk) {
+  GemmShape s{};
+  s.m = static_cast<int32_t>(e.m);
+  s.n_hat = static_cast<int32_t>(e.n_hat);
+  s.k_hat = static_cast<int32_t>(e.k_hat);
+  s.k0 = static_cast<int32_t>(chunk * kChunk);
+  s.klen = static_cast<int32_t>(e.k_hat - s.k0 < kChunk ? e.k_hat - s.k0 : kChunk);
+  s.batches = static_cast<int32_t>(e.b);
+  s.planes = static_cast<int32_t>(mods * e.b);
+  s.mod0 = mod0;
+  s.add = chunk > 0;
+  for (int i = 0; i < mods; ++i) {
+    const uint32_t p = static_cast<uint32_t>(kModuli[mod0 + i]);
+    s.p[i] = p;
+    s.magic[i] = static_cast<uint32_t>((uint64_t{1} << 32) / p);
+    s.bias[i] = static_cast<uint32_t>(((uint64_t{1} << 31) + p - 1) / p * p);
+  }
+  return s;
+}
+
+bool& use_reference_gemm() {
+  static bool v = false;  // verification hook only
+  return v;
+}
+
+imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
+                              const double* B, double beta, double* C, void* ws,
+                              cudaStream_t stream) {
+  const ExecPlan& e = plan.exec;
+  char* base = static_cast<char*>(ws);
+  auto region = [&](int r) { return base + e.layout.offset[r]; };
+  const int64_t* vec = e.vec_resident ? static_cast<const int64_t*>(plan.vec_dev)
+                                      : reinterpret_cast<const int64_t*>(region(IMD_REGION_VEC));
+  if (!e.vec_resident)
+    if (generate_vectors(e, const_cast<int64_t*>(vec), stream) != IMD_STATUS_SUCCESS)
+      return IMD_STATUS_CUDA_ERROR;
+  const Vectors v = split_vectors(vec, e);
+
+  if (alpha == 0.0 || e.k == 0 || e.path == Path::kDirect) {
+    EpilogueOnlyParams p{A, B, C, v, e.m, e.n, e.k, e.b, alpha, beta};
+    const unsigned int grid = grid_for(e.b * e.m * e.n, 1 << 20);
+    if (alpha == 0.0 || e.k == 0) k_beta<<<grid, kThreads, 0, stream>>>(p);
+    else k_direct<<<grid, kThreads, 0, stream>>>(p);
+    return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+  }
+
+  int16_t* sA = reinterpret_cast<int16_t*>(region(IMD_REGION_SA));
+  int16_t* sB = reinterpret_cast<int16_t*>(region(IMD_REGION_SB));
+  uint8_t* fA = reinterpret_cast<uint8_t*>(region(IMD_REGION_FA));
+  uint8_t* fB = reinterpret_cast<uint8_t*>(region(IMD_REGION_FB));
+  int8_t* RA = reinterpret_cast<int8_t*>(region(IMD_REGION_RA));
+  int8_t* RB = reinterpret_cast<int8_t*>(region(IMD_REGION_RB));
+  uint8_t* W = reinterpret_cast<uint8_t*>(region(IMD_REGION_W));
+
+  for (int x = 0; x < 2; ++x) {
+    ScaleParams p{};
+    p.X = x == 0 ? A : B;
+    p.row = x == 0 ? v.a_row : v.b_col;
+    p.kv = x == 0 ? v.a_k : v.b_k;
+    p.bat = x == 0 ? v.a_bat : v.b_bat;
+    p.rows = x == 0 ? e.m : e.n;
+    p.batches = e.b;
+    p.k = e.k;
+    p.rows_fast = e.rows_fast[x];
+    p.lg_rt = scale_lg_rt(e.rows_fast[x], e.k);
+    p.lhs_shift = e.lhs_shift;
+    p.rhs = e.rhs;
+    p.sigma = x == 0 ? sA : sB;
+    p.flag = x == 0 ? fA : fB;
+    const int64_t rt = int64_t{1} << p.lg_rt;
+    const int64_t blocks = (p.rows * p.batches + rt - 1) / rt;
+    k_scale<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(p);
+    if (!launched()) return IMD_STATUS_CUDA_ERROR;
+  }
+
+  const ResidueTables& rt = plan.res;
+  GemmPlanInfo info;
+  info.encode_tiled = plan.encode_tiled;
+  info.error_word = static_cast<unsigned int*>(plan.error_word);
+  info.sms = plan.sms;
+  for (int g0 = 0; g0 < e.N; g0 += e.g) {
+    const int mods = e.N - g0 < e.g ? e.N - g0 : e.g;
+    for (int x = 0; x < 2; ++x) {
+      ResidueParams p{};
+      p.X = x == 0 ? A : B;
+      p.row = x == 0 ? v.a_row : v.b_col;
+      p.kv = x == 0 ? v.a_k : v.b_k;
+      p.bat = x == 0 ? v.a_bat : v.b_bat;
+      p.rows = x == 0 ? e.m : e.n;
+      p.rows_pad = x == 0 ? e.m : e.n_hat;
+      p.batches = e.b;
+      p.k = e.k;
+      p.k_hat = e.k_hat;
+      p.rows_fast = e.rows_fast[x];
+      p.trunc = e.trunc;
+      p.mod0 = g0;
+      p.mods = mods;
+      p.sigma = x == 0 ? sA : sB;
+      p.R = x == 0 ? RA : RB;
+      p.t = rt;
+      const unsigned int grid = grid_for(p.rows_pad * p.batches * (p.k_hat >> 4));
+      if (rt.words == 2) k_residues<2><<<grid, kThreads, 0, stream>>>(p);
+      else k_residues<3><<<grid, kThreads, 0, stream>>>(p);
+      if (!launched()) return IMD_STATUS_CUDA_ERROR;
+    }
+    for (int64_t c = 0; c < e.k_chunks; ++c) {
+      const GemmShape s = gemm_shape(e, g0, mods, static_cast<int>(c));
+      const imd_status_t st = use_reference_gemm() ? gemm_reference_launch(s, RA, RB, W, stream)
+                                                   : gemm_launch(info, s, RA, RB, W, stream);
+      if (st != IMD_STATUS_SUCCESS) return st;
+    }
+  }
+
+  CrtParams p{};
+  p.W = W;
+  p.sigma = sA, p.tau = sB, p.fA = fA, p.fB = fB;
+  p.A = A, p.B = B, p.C = C;
+  p.v = v;
+  p.m = e.m, p.n = e.n, p.n_hat = e.n_hat, p.k = e.k, p.b = e.b;
+  p.alpha = alpha, p.beta = beta;
+  p.t = plan.crt;
+  const unsigned int grid = grid_for(e.b * e.m * (e.n_hat >> 2));
+  switch (plan.crt.limbs) {
+    case 1: k_crt<1><<<grid, kThreads, 0, stream>>>(p); break;
+    case 2: k_crt<2><<<grid, kThreads, 0, stream>>>(p); break;
+    case 3: k_crt<3><<<grid, kThreads, 0, stream>>>(p); break;
+    case 4: k_crt<4><<<grid, kThreads, 0, stream>>>(p); break;
+    default: k_crt<5><<<grid, kThreads, 0, stream>>>(p); break;
+  }
+  return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+}  // namespace imd

@@ -94,9 +94,11 @@ struct imd_plan_st {
   imd::TensorCopy A, B, C;   // the caller's descriptors (aliasing intervals)
   imd::ExecPlan exec;
   imd::CrtTables crt{};
+  imd::ResidueTables res{};
   int device = 0;
   int sms = 0;
   void* vec_dev = nullptr;   // IMD_VEC_RESIDENT: plan-owned scatter vectors
   void* encode_tiled = nullptr;  // driver entry point for TMA descriptor encoding
+  void* error_word = nullptr;    // device address of the sticky error word of bounded waits
   std::vector<int64_t> slot_key[2];
 };
