@@ -1,0 +1,392 @@
+"""Benchmark of the emulated FP64 contraction path (imd_plan_create -> imd_contract).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line. Metric: FP64-equivalent TFLOPS = 2 b m n k / t (the reference's definition,
+docs/BENCHMARKING.md:16) on 'kjbc,kiac->abij' with a=b=c=200, i=j=k=40 (GEMM view 8000^3), N = 14
+moduli, residue group 7, alpha = 1, beta = 0, seeded synthetic uniform [-1, 1) operands.
+
+  value  device-resident operands, CUDA events on the launching stream, max over ranks
+  e2e    the same call through the Python front end with HOST operands: pinned host -> device
+         copies of A and B and the device -> host copy of C inside the timed region
+  roofline      the tcgen05 int8 GEMM phase (algorithmic int8 ops 2 N b m n k over its measured time)
+  cpu_baseline  the CPU oracle (oracle/, a port of the reference's specification) on a sampled block
+  --impl reference  times that CPU oracle alone, all host threads (the reference has no other CPU
+         implementation that can travel to the GPU box: its own is Python, spec/oracle.py)
+
+With N > 1 ranks (torchrun) the output C is partitioned over its free modes a and b; every rank
+holds the operand slabs of its tile and computes it with its own plan (no data-path collective:
+the slabs a rank needs are resident), strong scaling of the one contraction.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (spec, extents, N, g)
+    "cc8000": ("kjbc,kiac->abij", dict(a=200, b=200, c=200, i=40, j=40, k=40), 14, 7),
+    "cc1000": ("kjbc,kiac->abij", dict(a=50, b=50, c=50, i=20, j=20, k=20), 14, 7),
+}
+GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}  # ranks over (a, b)
+SEED = 20251125
+MASK = (1 << 64) - 1
+
+
+# ------------------------------------------------------------------ synthetic data (counter based)
+def mix_np(idx, seed):
+    """splitmix64 of (seed + flat index) -> uniform [-1, 1) float64; numpy, uint64 wraparound."""
+    z = (idx.astype(np.uint64) + np.uint64(seed)) * np.uint64(0x9E3779B97F4A7C15)
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    z = z ^ (z >> np.uint64(31))
+    return (z >> np.uint64(11)).astype(np.float64) * (2.0 ** -52) - 1.0
+
+
+def mix_torch(idx, seed):
+    """The same function on the GPU: int64 arithmetic wraps like uint64; shifts made logical."""
+    import torch
+
+    def i64(v):
+        v &= MASK
+        return v - (1 << 64) if v >= (1 << 63) else v
+
+    def shr(z, s):
+        return (z >> s) & ((1 << (64 - s)) - 1)
+    z = (idx + i64(seed)) * i64(0x9E3779B97F4A7C15)
+    z = (z ^ shr(z, 30)) * i64(0xBF58476D1CE4E5B9)
+    z = (z ^ shr(z, 27)) * i64(0x94D049BB133111EB)
+    z = z ^ shr(z, 31)
+    return shr(z, 11).to(torch.float64) * (2.0 ** -52) - 1.0
+
+
+def slab_offsets_torch(extent, full_extent, start, device):
+    """Flat offsets (in the FULL dense tensor) of the slab [start, start + extent) per mode."""
+    import torch
+    strides, acc = [], 1
+    for e in reversed(full_extent):
+        strides.append(acc)
+        acc *= e
+    strides = list(reversed(strides))
+    off = torch.zeros((), dtype=torch.int64, device=device)
+    for d, (e, s0, st) in enumerate(zip(extent, start, strides)):
+        shape = [1] * len(extent)
+        shape[d] = e
+        off = off + (torch.arange(s0, s0 + e, dtype=torch.int64, device=device) * st).reshape(shape)
+    return off
+
+
+class Problem:
+    """The contraction of one rank: its slab extents and where they sit in the full tensors."""
+
+    def __init__(self, workload, rank, world):
+        self.spec, self.ext, self.N, self.g = WORKLOADS[workload]
+        self.labels = [s for s in self.spec.replace("->", ",").split(",")]
+        pa, pb = GRID[world]
+        ra, rb = rank // pb, rank % pb
+        self.full = dict(self.ext)
+        self.start = {c: 0 for c in self.ext}
+        self.local = dict(self.ext)
+        for lab, parts, r in (("a", pa, ra), ("b", pb, rb)):
+            lo = self.ext[lab] * r // parts
+            hi = self.ext[lab] * (r + 1) // parts
+            self.start[lab], self.local[lab] = lo, hi - lo
+        self.seeds = [SEED, SEED + 1]
+
+    def shape(self, x, local=True):
+        e = self.local if local else self.full
+        return [e[c] for c in self.labels[x]]
+
+    def flops_eq_full(self):
+        e = self.full
+        return 2.0 * math.prod(e[c] for c in set("".join(self.labels)))
+
+    def device_operand(self, x, device):
+        off = slab_offsets_torch(self.shape(x), self.shape(x, False),
+                                 [self.start[c] for c in self.labels[x]], device)
+        return mix_torch(off, self.seeds[x]).contiguous()
+
+
+# ------------------------------------------------------------------ CPU oracle (baseline / reference arm)
+def cpu_sample(prob, rows, cols, threads=None):
+    """Time the CPU oracle on a rows x cols block of outputs (full k) of the FULL problem.
+    Returns (seconds, flops_eq of the block, block result, row ids, col ids)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import imd_oracle as orc
+    labels = prob.labels
+    descs = []
+    for x in range(3):
+        ext = prob.shape(x, False)
+        st, acc = [], 1
+        for e in reversed(ext):
+            st.append(acc)
+            acc *= e
+        descs.append(orc.Desc(ext, list(reversed(st)), [ord(c) for c in labels[x]]))
+    view = orc.lower(*descs)
+    rng = np.random.default_rng(5)
+    ri = np.sort(rng.choice(view.m, size=min(rows, view.m), replace=False))
+    cj = np.sort(rng.choice(view.n, size=min(cols, view.n), replace=False))
+    seedA, seedB = (prob.seeds[1], prob.seeds[0]) if view.swapped else (prob.seeds[0], prob.seeds[1])
+    offA = orc.vec(view, "A_row")[ri][:, None] + orc.vec(view, "A_k")[None, :]
+    offB = orc.vec(view, "B_col")[cj][:, None] + orc.vec(view, "B_k")[None, :]
+    Ab, Bb = mix_np(offA, seedA), mix_np(offB, seedB)
+    t0 = time.perf_counter()
+    out = orc.gemm(Ab, Bb, prob.N)
+    dt = time.perf_counter() - t0
+    coff = orc.vec(view, "C_row")[ri][:, None] + orc.vec(view, "C_col")[None, cj]
+    return dt, 2.0 * len(ri) * len(cj) * view.k, out, coff
+
+
+def cpu_threads():
+    n = os.environ.get("OMP_NUM_THREADS")
+    return int(n) if n else (os.cpu_count() or 1)
+
+
+def run_reference(args, rank):
+    """The reference arm: the CPU oracle port, all host threads, on bounded samples of the workload."""
+    if rank != 0:
+        return
+    prob = Problem(args.workload, 0, 1)
+    side = 384
+    times = []
+    for it in range(args.warmup + args.steps):
+        dt, fl, _, _ = cpu_sample(prob, side, side)
+        if it >= args.warmup:
+            times.append(dt)
+    t = float(np.mean(times))
+    val = fl / t / 1e12
+    line = dict(metric="fp64_equivalent_tflops", value=val, unit="TFLOPS-eq", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=t * 1e3, higher_is_better=True,
+                scaling="strong", vs_baseline=None, dtype="int8xint8->int32 (FP64 emulation)",
+                data="synthetic", impl="reference",
+                config=dict(workload=f"{args.workload}: {prob.spec} {prob.ext} N={prob.N}",
+                            note="CPU oracle port of the reference specification; each step is a "
+                                 f"{side}x{side} output block with full k"),
+                cpu_baseline=dict(value=val, unit="TFLOPS-eq", cores=cpu_threads(), kind="port",
+                                  sample=f"{side}x{side} outputs x k, {args.steps} steps"),
+                e2e=dict(value=val, unit="TFLOPS-eq", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler(threading.Thread):
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], False
+
+    def run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def summary(self):
+        self.stop_flag = True
+        if not self.samples:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unavailable"])
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None,
+                    sm_max_mhz=int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
+                    reasons=reasons, samples=len(self.samples))
+
+
+# ------------------------------------------------------------------ our arm
+def run_ours(args, rank, world, local_rank):
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    import immerdink_b200 as imd
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    prob = Problem(args.workload, rank, world)
+    lib = imd.load_library()
+
+    A = prob.device_operand(0, dev)
+    B = prob.device_operand(1, dev)
+    Cd = torch.empty(prob.shape(2), dtype=torch.float64, device=dev)
+    plan = imd.Plan(prob.spec, A, B, Cd, N=prob.N, g=prob.g)
+    ws = torch.empty(plan.workspace_bytes + 256, dtype=torch.uint8, device=dev)
+    off = (-ws.data_ptr()) % 256
+    wsv = ws[off:off + plan.workspace_bytes]
+    stream = torch.cuda.current_stream()
+    low = plan.lowering
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
+
+    def step():
+        plan.contract(A, B, Cd, workspace=wsv, stream=stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- device-resident timing with per-phase events
+    lib.lib.imd_prof_enable(64 * (args.steps + 1))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(args.steps)]
+    barrier()
+    for s in range(args.steps):
+        flush.fill_(s)  # evict the previous step's working set from L2 (outside the timed events)
+        ev[s][0].record(stream)
+        step()
+        ev[s][1].record(stream)
+    barrier()
+    clocks = sampler.summary()
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    phases = (C.c_float * 8)()
+    lib.lib.imd_prof_read(phases, 8)
+    lib.lib.imd_prof_enable(0)
+    phase_ms = {name: phases[t] / args.steps for t, name in
+                ((1, "vectors+scale"), (2, "residues"), (3, "gemm"), (4, "crt"))}
+    t_ms = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    ms_max = float(t_ms.item())
+
+    # ---- end to end: pinned host operands in, host result out, through the public Python API
+    hA = torch.empty(A.shape, dtype=torch.float64).pin_memory()
+    hB = torch.empty(B.shape, dtype=torch.float64).pin_memory()
+    hC = torch.empty(Cd.shape, dtype=torch.float64).pin_memory()
+    hA.copy_(A)
+    hB.copy_(B)
+    dA2, dB2 = torch.empty_like(A), torch.empty_like(B)
+
+    def e2e_step():
+        dA2.copy_(hA, non_blocking=True)
+        dB2.copy_(hB, non_blocking=True)
+        imd.contract(prob.spec, dA2, dB2, Cd, N=prob.N, g=prob.g, workspace=wsv, stream=stream)
+        hC.copy_(Cd, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    t_e2e = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t_e2e.item())
+    err = lib.lib.imd_test_device_error()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    flops = prob.flops_eq_full()
+    # the int8 GEMM phase of this rank against the measured dense tensor peak
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    bf16 = peaks.get("bf16_tflops_sustained")
+    peak_tops = 2.0 * bf16 if bf16 else 2.0 * 1400.0  # dense int8 = 2 x dense bf16 on this part
+    gemm_ops = 2.0 * prob.N * low["b"] * low["m"] * low["n"] * low["k"]
+    achieved = gemm_ops / (phase_ms["gemm"] * 1e-3) / 1e12 if phase_ms["gemm"] > 0 else 0.0
+    line = dict(metric="fp64_equivalent_tflops", value=flops / (ms_max * 1e-3) / 1e12, unit="TFLOPS-eq",
+                n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms_max,
+                higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="int8xint8->int32 (FP64 emulation)", data="synthetic",
+                config=dict(workload=f"{args.workload}: {prob.spec} {prob.ext} N={prob.N} g={prob.g} "
+                                     "alpha=1 beta=0, uniform[-1,1)",
+                            partition=f"C modes (a,b) over {GRID[world]} ranks, slabs resident",
+                            l2="256 MB buffer written between timed steps",
+                            gemm_view=[low["m"], low["n"], low["k"], low["b"]]),
+                e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOPS-eq",
+                         h2d_bytes_per_step=(A.numel() + B.numel()) * 8 * world,
+                         d2h_bytes_per_step=Cd.numel() * 8 * world, ms_per_step=e2e_ms),
+                gpu_launches=int(low["kernel_launches"]) * args.steps,
+                clocks=clocks,
+                phases_ms=phase_ms,
+                roofline=dict(bound="tensor", achieved=achieved, peak=peak_tops, unit="TOP/s (int8)",
+                              frac=achieved / peak_tops, traffic=None,
+                              note="peak = 2 x measured sustained dense bf16 (of measured)" if bf16
+                              else "peak = 2 x 1400 TFLOP/s bf16 (of fallback)"),
+                device_error=int(err))
+    if world == 1 and not args.no_cpu:
+        # DGEMM on the same GPU, same GEMM view
+        n = low["m"]
+        x = torch.rand(n, low["k"], dtype=torch.float64, device=dev)
+        y = torch.rand(low["k"], low["n"], dtype=torch.float64, device=dev)
+        torch.matmul(x, y)
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record()
+        for _ in range(3):
+            torch.matmul(x, y)
+        d1.record()
+        torch.cuda.synchronize()
+        line["native_dgemm_tflops"] = 3 * 2.0 * n * low["k"] * low["n"] / (d0.elapsed_time(d1) * 1e-3) / 1e12
+        del x, y
+        # CPU oracle on a sampled block; the same block checks the GPU result bit for bit
+        side = 64
+        dt, _, _, _ = cpu_sample(prob, side, side)
+        side = int(max(64, min(1024, side * math.sqrt(12.0 / max(dt, 1e-3)))))
+        dt, fl, out, coff = cpu_sample(prob, side, side)
+        got = Cd.reshape(-1)[torch.from_numpy(coff.reshape(-1)).to(dev)].cpu().numpy().reshape(out.shape)
+        line["parity_sample"] = dict(outputs=int(out.size),
+                                     bit_exact=bool(np.array_equal(got.view(np.uint64), out.view(np.uint64))))
+        line["cpu_baseline"] = dict(value=fl / dt / 1e12, unit="TFLOPS-eq", cores=cpu_threads(), kind="port",
+                                    sample=f"{side}x{side} outputs x k={low['k']} ({dt:.1f} s)")
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cc8000", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and DGEMM legs")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world not in GRID:
+        raise SystemExit(f"unsupported number of ranks {world}")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -50,6 +50,10 @@ imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stre
 // Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.
 bool& use_reference_gemm();
 
+// Benchmark-only phase timing (tags: 1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate path).
+int profile_enable(int capacity);
+int profile_read(float* ms_by_tag, int tags);
+
 // Sticky device-side error word (bounded waits that gave up); read by the verification hook.
 unsigned int* device_error_word();
 

@@ -14,6 +14,7 @@
 // (src/contract.cu:1334-1485) and its kernels K0, K1, K2/K3, KF, KL, K5, k_direct,
 // k5_beta_only; the numerics are in numerics.cuh.
 #include <cstdint>
+#include <vector>
 
 #include "kernels.hpp"
 #include "numerics.cuh"
@@ -423,12 +424,60 @@ bool& use_reference_gemm() {
   return v;
 }
 
+// Phase timing for the benchmark: when enabled, enqueue_contract records an event from a
+// preallocated pool on the caller's stream at every phase boundary. Off by default; one caller
+// at a time (the pool is process-global).
+namespace {
+struct PhaseProfile {
+  std::vector<cudaEvent_t> events;
+  std::vector<int> tags;
+  size_t used = 0;
+  bool on = false;
+} g_prof;
+void mark(int tag, cudaStream_t stream) {
+  if (!g_prof.on || g_prof.used >= g_prof.events.size()) return;
+  cudaEventRecord(g_prof.events[g_prof.used], stream);
+  g_prof.tags[g_prof.used++] = tag;
+}
+}  // namespace
+
+int profile_enable(int capacity) {
+  for (cudaEvent_t e : g_prof.events) cudaEventDestroy(e);
+  g_prof = PhaseProfile{};
+  if (capacity <= 0) return 0;
+  g_prof.events.resize(static_cast<size_t>(capacity));
+  g_prof.tags.assign(static_cast<size_t>(capacity), 0);
+  for (cudaEvent_t& e : g_prof.events)
+    if (cudaEventCreate(&e) != cudaSuccess) return 1;
+  g_prof.on = true;
+  return 0;
+}
+
+// ms_by_tag[t] += time of every segment that ENDS with an event tagged t; returns segments read.
+int profile_read(float* ms_by_tag, int tags) {
+  if (!g_prof.on || g_prof.used == 0) return 0;
+  cudaEventSynchronize(g_prof.events[g_prof.used - 1]);
+  int n = 0;
+  for (size_t i = 1; i < g_prof.used; ++i) {
+    const int t = g_prof.tags[i];
+    if (t <= 0 || t >= tags) continue;  // tag 0 opens a call: nothing ends there
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, g_prof.events[i - 1], g_prof.events[i]) == cudaSuccess) {
+      ms_by_tag[t] += ms;
+      ++n;
+    }
+  }
+  g_prof.used = 0;
+  return n;
+}
+
 imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
                               const double* B, double beta, double* C, void* ws,
                               cudaStream_t stream) {
   const ExecPlan& e = plan.exec;
   char* base = static_cast<char*>(ws);
   auto region = [&](int r) { return base + e.layout.offset[r]; };
+  mark(0, stream);
   const int64_t* vec = e.vec_resident ? static_cast<const int64_t*>(plan.vec_dev)
                                       : reinterpret_cast<const int64_t*>(region(IMD_REGION_VEC));
   if (!e.vec_resident)
@@ -441,6 +490,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     const unsigned int grid = grid_for(e.b * e.m * e.n, 1 << 20);
     if (alpha == 0.0 || e.k == 0) k_beta<<<grid, kThreads, 0, stream>>>(p);
     else k_direct<<<grid, kThreads, 0, stream>>>(p);
+    mark(5, stream);
     return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
   }
 
@@ -473,6 +523,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     if (!launched()) return IMD_STATUS_CUDA_ERROR;
   }
 
+  mark(1, stream);
   const ResidueTables& rt = plan.res;
   GemmPlanInfo info;
   info.encode_tiled = plan.encode_tiled;
@@ -503,12 +554,14 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
       else k_residues<3><<<grid, kThreads, 0, stream>>>(p);
       if (!launched()) return IMD_STATUS_CUDA_ERROR;
     }
+    mark(2, stream);
     for (int64_t c = 0; c < e.k_chunks; ++c) {
       const GemmShape s = gemm_shape(e, g0, mods, static_cast<int>(c));
       const imd_status_t st = use_reference_gemm() ? gemm_reference_launch(s, RA, RB, W, stream)
                                                    : gemm_launch(info, s, RA, RB, W, stream);
       if (st != IMD_STATUS_SUCCESS) return st;
     }
+    mark(3, stream);
   }
 
   CrtParams p{};
@@ -527,6 +580,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     case 4: k_crt<4><<<grid, kThreads, 0, stream>>>(p); break;
     default: k_crt<5><<<grid, kThreads, 0, stream>>>(p); break;
   }
+  mark(4, stream);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
 

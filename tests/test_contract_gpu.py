@@ -38,18 +38,23 @@ def test_golden_matrix(case, reference_gemm):
     if case["traced"] and emulated:
         lay = gu.layout_of(descs, N, rounding=rnd)
         kh, nh = plan.lowering["k_hat"], plan.lowering["n_hat"]
-        sig = ws.region(lay["sA"][0], 2 * m, np.int16)
-        tau = ws.region(lay["sB"][0], 2 * n, np.int16)
-        assert np.array_equal(sig, ZM[key + "_sigma"]) and np.array_equal(tau, ZM[key + "_tau"])
-        assert np.array_equal(ws.region(lay["fA"][0], m, np.uint8), ZM[key + "_fA"])
-        assert np.array_equal(ws.region(lay["fB"][0], n, np.uint8), ZM[key + "_fB"])
-        RA = ws.region(lay["RA"][0], N * m * kh, np.int8).reshape(N, m, kh)
+        g = {x: ZM[key + "_" + x] for x in ("sigma", "tau", "fA", "fB", "RA", "RB", "W")}
+        mm, nn = m, n
+        if plan.lowering["swapped"]:  # the GEMM computes C^T: the roles of A and B are exchanged
+            mm, nn = n, m
+            g = dict(sigma=g["tau"], tau=g["sigma"], fA=g["fB"], fB=g["fA"], RA=g["RB"], RB=g["RA"],
+                     W=g["W"].transpose(0, 2, 1))
+        assert np.array_equal(ws.region(lay["sA"][0], 2 * mm, np.int16), g["sigma"])
+        assert np.array_equal(ws.region(lay["sB"][0], 2 * nn, np.int16), g["tau"])
+        assert np.array_equal(ws.region(lay["fA"][0], mm, np.uint8), g["fA"])
+        assert np.array_equal(ws.region(lay["fB"][0], nn, np.uint8), g["fB"])
+        RA = ws.region(lay["RA"][0], N * mm * kh, np.int8).reshape(N, mm, kh)
         RB = ws.region(lay["RB"][0], N * nh * kh, np.int8).reshape(N, nh, kh)
-        assert np.array_equal(RA[:, :, :k], ZM[key + "_RA"]) and not RA[:, :, k:].any()
-        assert np.array_equal(RB[:, :n, :k], ZM[key + "_RB"])
-        assert not RB[:, n:, :].any() and not RB[:, :, k:].any()
-        W = ws.region(lay["W"][0], N * m * nh, np.uint8).reshape(N, m, nh)
-        assert np.array_equal(W[:, :, :n], ZM[key + "_W"])
+        assert np.array_equal(RA[:, :, :k], g["RA"]) and not RA[:, :, k:].any()
+        assert np.array_equal(RB[:, :nn, :k], g["RB"])
+        assert not RB[:, nn:, :].any() and not RB[:, :, k:].any()
+        W = ws.region(lay["W"][0], N * mm * nh, np.uint8).reshape(N, mm, nh)
+        assert np.array_equal(W[:, :, :nn], g["W"])
     plan.close()
 
 
