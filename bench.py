@@ -35,6 +35,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: (spec, extents, N, g)
     "cc8000": ("kjbc,kiac->abij", dict(a=200, b=200, c=200, i=40, j=40, k=40), 14, 7),
+    "cc4000": ("kjbc,kiac->abij", dict(a=100, b=100, c=100, i=40, j=40, k=40), 14, 7),
     "cc1000": ("kjbc,kiac->abij", dict(a=50, b=50, c=50, i=20, j=20, k=20), 14, 7),
 }
 GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}  # ranks over (a, b)
@@ -179,36 +180,41 @@ def run_reference(args, rank):
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler(threading.Thread):
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, sampled through NVML while the timed region runs."""
 
     def __init__(self, index):
         super().__init__(daemon=True)
-        self.index, self.samples, self.stop_flag = index, [], False
+        self.index, self.samples, self.stop_flag, self.max_mhz = index, [], False, None
+        self.error = None
 
     def run(self):
-        while not self.stop_flag:
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
-                                     timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([x.strip() for x in out.split(",")])
-            except Exception:
-                pass
-            time.sleep(0.05)
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
+            h = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            while not self.stop_flag:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                                     nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)))
+                time.sleep(0.002)
+        except Exception as exc:  # NVML missing: report it, never fail the benchmark
+            self.error = repr(exc)
 
     def summary(self):
         self.stop_flag = True
+        self.join(timeout=2)
         if not self.samples:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unavailable"])
-        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return dict(sm_mhz=sm[len(sm) // 2] if sm else None,
-                    sm_max_mhz=int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
-                    reasons=reasons, samples=len(self.samples))
+            return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=["unavailable: " + str(self.error)])
+        sm = sorted(s[0] for s in self.samples)
+        bits = 0
+        for _, r in self.samples:
+            bits |= r
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                 0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+        return dict(sm_mhz=sm[len(sm) // 2], sm_min_mhz=sm[0], sm_max_mhz=self.max_mhz,
+                    reasons=[n for b, n in names.items() if bits & b], samples=len(self.samples))
 
 
 # ------------------------------------------------------------------ our arm
@@ -371,7 +377,7 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cc8000", choices=sorted(WORKLOADS))
