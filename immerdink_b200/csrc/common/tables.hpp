@@ -16,7 +16,6 @@ constexpr int kFracBits = 60;            // fixed-point fraction bits of the sum
 constexpr int64_t kChunkMax = 131071;    // floor((2^31 - 1) / 128^2): int32 cannot overflow
 constexpr int64_t kChunk = 130944;       // chunk length used: 1023 K blocks of 128 (<= kChunkMax)
 constexpr int kRegionAlign = 256;
-constexpr int kCrtLimbs = 5;             // 32-bit limbs of the widest unreduced CRT sum (N P < 2^160)
 constexpr int kBigLimbs = 10;            // 320-bit scratch for plan-time arithmetic
 
 constexpr int kModuli[kMaxModuli] = {256, 255, 253, 251, 247, 241, 239, 233, 229, 227,
@@ -24,29 +23,39 @@ constexpr int kModuli[kMaxModuli] = {256, 255, 253, 251, 247, 241, 239, 233, 229
 
 using Big = Wide<kBigLimbs>;
 
-// Everything the kernels need for one N; passed to kernels by value inside their parameters.
+// Everything the CRT kernel needs for one N; passed by value inside the kernel parameters.
+// The unreduced sum S = sum_l M_l y_l is accumulated on `nl` carry-free limbs of `lw` bits (each
+// limb sum stays below 2^32), then normalised to `words` 32-bit words.
+constexpr int kCrtWords = 6;     // 32-bit words of the widest S (N P < 2^160, limbs up to 171 bits)
+constexpr int kCrtMaxLimbs = 9;
 struct CrtTables {
   int32_t N;
-  int32_t limbs;                       // 32-bit limbs that hold N * P
+  int32_t nl, lw;                      // limbs and limb width: 20 bits for N <= 16, else 19
+  int32_t words;                       // 32-bit words = ceil(nl * lw / 32)
+  int32_t qshift;                      // S >> qshift and rinv give the multiple of P to subtract
+  uint32_t rinv;                       // floor(2^(qshift + 57 - ...) / P), see crt_tables()
+  int32_t rshift;                      // final right shift of umulhi(S >> qshift, rinv)
   uint32_t p[kMaxModuli];
-  uint32_t q[kMaxModuli];              // M_l^-1 mod p_l
-  uint32_t magic[kMaxModuli];          // ceil(2^32 / p_l): floor(v / p) = umulhi(v, magic), v < 2^24
-  uint32_t frac[kMaxModuli];           // floor(2^27 / p_l): fixed-point 1 / p_l for the quotient estimate
-  uint32_t M[kMaxModuli][kCrtLimbs];   // P / p_l
-  uint32_t P[kCrtLimbs];
-  uint32_t H[kCrtLimbs];               // P / 2 - 1: the largest representable |z|
+  uint32_t q[kMaxModuli];              // M_l^-1 mod p_l (applied by the GEMM epilogue)
+  uint32_t M[kMaxModuli][kCrtMaxLimbs];  // limbs of P / p_l
+  uint32_t P[kCrtWords];
+  uint32_t H[kCrtWords];               // P / 2 - 1: the largest representable |z|
 };
 
 // Constants of the residue emitter for one N (uniform across a warp: kernels take them by value
-// and read them from the constant bank).
+// and read them from the constant bank). The quantised integer is split into signed base-256
+// digits d_j in [-128, 127]; s = sum_j d_j w_j with signed weights w_j = SMod(256^j, p) is formed
+// by dp4a on top of `lift`, a multiple of p that keeps the sum positive; u = (s + lift) mod p is
+// the nonnegative residue, and the symmetric representative is u - p when u > ceil(p / 2) - 1.
 struct ResidueTables {
   int32_t N;
-  int32_t words;                         // 32-bit words of |a'|: 2 (N <= 16) or 3
+  int32_t words;                         // 32-bit words of the quantised integer: 2 (N <= 16) or 3
   uint32_t p[kMaxModuli];
-  uint32_t half[kMaxModuli];             // floor(p / 2)
-  uint32_t magic[kMaxModuli];            // ceil(2^32 / p)
-  uint32_t lift[kMaxModuli];             // a multiple of p >= 2^20: makes negated sums nonnegative
-  uint32_t weight[3][kMaxModuli];        // 4 packed byte weights 2^(8 (4 j + i)) mod p
+  uint32_t magic[kMaxModuli];            // ceil(2^32 / p): floor(v / p) = umulhi(v, magic), v < 2^24
+  uint32_t lift[kMaxModuli];             // multiple of p, >= 2^18 > max |s|
+  uint32_t fix_add[kMaxModuli];          // (127 - (ceil(p/2) - 1)) in every byte
+  uint32_t fix_mul[kMaxModuli];          // 256 - p (0 for p = 256): added to bytes above the half
+  uint32_t weight[3][kMaxModuli];        // 4 packed signed weights SMod(256^(4 j + i), p)
 };
 
 inline ResidueTables residue_tables(int N) {
@@ -56,14 +65,17 @@ inline ResidueTables residue_tables(int N) {
   for (int l = 0; l < N; ++l) {
     const uint32_t p = static_cast<uint32_t>(kModuli[l]);
     t.p[l] = p;
-    t.half[l] = p / 2;
     t.magic[l] = static_cast<uint32_t>(((uint64_t{1} << 32) + p - 1) / p);
-    t.lift[l] = ((1u << 20) + p - 1) / p * p;
+    t.lift[l] = ((1u << 18) + p - 1) / p * p;
+    const uint32_t top = (p + 1) / 2 - 1;  // largest nonnegative symmetric residue
+    t.fix_add[l] = (127u - top) * 0x01010101u;
+    t.fix_mul[l] = 256u - p;
     uint32_t pw = 1 % p;
     for (int j = 0; j < 3; ++j) {
       uint32_t word = 0;
       for (int i = 0; i < 4; ++i) {
-        word |= pw << (8 * i);
+        const int sym = static_cast<int>((pw + p / 2) % p) - static_cast<int>(p / 2);
+        word |= (static_cast<uint32_t>(sym) & 0xFFu) << (8 * i);
         pw = (pw * 256u) % p;
       }
       t.weight[j][l] = word;
@@ -90,19 +102,45 @@ inline CrtTables crt_tables(int N) {
   const PlanConstants c = plan_constants(N);
   t.N = N;
   const Big NP = wide_mul_small(c.P, static_cast<uint32_t>(N));
-  t.limbs = (wide_bitlen(NP) + 31) / 32;
-  for (int i = 0; i < kCrtLimbs; ++i) {
+  t.lw = N <= 16 ? 20 : 19;
+  t.nl = (wide_bitlen(NP) + t.lw - 1) / t.lw;
+  t.words = (t.nl * t.lw + 31) / 32;
+  for (int i = 0; i < kCrtWords; ++i) {
     t.P[i] = c.P.w[i];
     t.H[i] = c.H.w[i];
+  }
+  // Quotient estimate: x_lo = ((S >> qshift) * rinv) >> (32 + rshift) <= S / P, within 2^-20.
+  // S >> qshift < 2^32 because S < N P < 2^(bitlen(P) + 5) and qshift = bitlen(P) - 27.
+  const int B = wide_bitlen(c.P);
+  t.qshift = B > 27 ? B - 27 : 0;
+  {
+    // rinv = floor(2^(qshift + F) / P) with F chosen so that rinv has 31 bits
+    int F = 31 + B - t.qshift;          // 2^(qshift + F) / P is about 2^(31 + (B - log2 P)) < 2^32
+    Big num = wide_shl(wide_u64<kBigLimbs>(1), t.qshift + F);
+    // long division by P via bitwise restoring division (plan time only)
+    Big quo = wide_zero<kBigLimbs>(), rem = wide_zero<kBigLimbs>();
+    for (int bit = wide_bitlen(num) - 1; bit >= 0; --bit) {
+      rem = wide_shl(rem, 1);
+      rem.w[0] |= (num.w[bit >> 5] >> (bit & 31)) & 1u;
+      if (wide_cmp(rem, c.P) >= 0) {
+        rem = wide_sub(rem, c.P);
+        quo.w[bit >> 5] |= 1u << (bit & 31);
+      }
+    }
+    while (quo.w[1] != 0) {  // keep it in 32 bits
+      quo = wide_shr(quo, 1);
+      --F;
+    }
+    t.rinv = quo.w[0];
+    t.rshift = F - 32;                  // x_lo 2^rshift = umulhi(S >> qshift, rinv)
   }
   for (int l = 0; l < N; ++l) {
     const uint32_t p = static_cast<uint32_t>(kModuli[l]);
     t.p[l] = p;
-    t.magic[l] = static_cast<uint32_t>(((uint64_t{1} << 32) + p - 1) / p);
-    t.frac[l] = (1u << 27) / p;
     Big M = c.P;
     wide_divmod_small(&M, p);
-    for (int i = 0; i < kCrtLimbs; ++i) t.M[l][i] = M.w[i];
+    for (int i = 0; i < t.nl; ++i)
+      t.M[l][i] = wide_shr(M, i * t.lw).w[0] & ((1u << t.lw) - 1);
     Big tmp = M;
     const uint32_t r = wide_divmod_small(&tmp, p);
     for (uint32_t x = 1; x < p; ++x)

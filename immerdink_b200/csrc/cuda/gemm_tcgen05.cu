@@ -1,6 +1,7 @@
 // Batched int8 GEMM with a modular epilogue on Blackwell tensor cores (sm_100a only).
 //
-//   W[l][lambda][i][j] = (sum_h RA[z][i][h] * RB[z][j][h]  (+ W))  mod p_l      z = slot * b + lambda
+//   W[l][lambda][i][j] = (q_l * sum_h RA[z][i][h] * RB[z][j][h]  (+ W))  mod p_l      z = slot * b + lambda
+//   (q_l = (P / p_l)^-1 mod p_l: the planes hold the CRT digits y_l directly)
 //
 // One persistent CTA per SM walks (plane, 128 x 256 tile) work items. Per CTA:
 //   warp 0   TMA producer: cp.async.bulk.tensor loads of 128-byte-swizzled K-major tiles of A
@@ -169,7 +170,8 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t* v) {
 
 // 16 accumulators -> 16 residues in [0, p), packed into a uint4 (column order = byte order).
 __device__ __forceinline__ uint4 reduce16(const uint32_t* acc, uint4 prev, bool add, uint32_t p,
-                                          uint32_t magic, uint32_t bias) {
+                                          uint32_t magic, uint32_t magic_up, uint32_t bias,
+                                          uint32_t q) {
   uint32_t out[4];
   const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
 #pragma unroll
@@ -177,11 +179,16 @@ __device__ __forceinline__ uint4 reduce16(const uint32_t* acc, uint4 prev, bool 
     uint32_t word = 0;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      uint32_t u = acc[4 * wd + b] + bias;             // in [0, 2^32): |acc| < 2^31 - 2^20
-      if (add) u += (pv[wd] >> (8 * b)) & 0xFFu;
+      const uint32_t u = acc[4 * wd + b] + bias;       // in [0, 2^32): |acc| < 2^31 - 2^20
       uint32_t r = u - __umulhi(u, magic) * p;         // in [0, 2 p)
       r = min(r, r - p);                               // unsigned wrap: r - p is huge when r < p
-      word |= r << (8 * b);
+      const uint32_t v = r * q;                        // < 2^16
+      uint32_t y = v - __umulhi(v, magic_up) * p;      // (q r) mod p, exact
+      if (add) {
+        y += (pv[wd] >> (8 * b)) & 0xFFu;              // both < p
+        y = min(y, y - p);
+      }
+      word |= y << (8 * b);
     }
     out[wd] = word;
   }
@@ -315,6 +322,7 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       tc_fence_after();
       const int slot = c.plane / p.s.batches, lam = c.plane % p.s.batches;
       const uint32_t pm = p.s.p[slot], magic = p.s.magic[slot], bias = p.s.bias[slot];
+      const uint32_t magic_up = p.s.magic_up[slot], qm = p.s.q[slot];
       const int row = c.tm * kTileM + quarter * 32 + lane;
       const int64_t wplane = static_cast<int64_t>(p.s.mod0 + slot) * p.s.batches + lam;
       uint8_t* wrow = p.W + (wplane * p.s.m + row) * static_cast<int64_t>(p.s.n_hat);
@@ -332,7 +340,7 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
               uint4* dst = reinterpret_cast<uint4*>(wrow + col + 16 * hf);
               uint4 prev = make_uint4(0, 0, 0, 0);
               if (p.s.add) prev = *dst;
-              *dst = reduce16(v + 16 * hf, prev, p.s.add != 0, pm, magic, bias);
+              *dst = reduce16(v + 16 * hf, prev, p.s.add != 0, pm, magic, magic_up, bias, qm);
             }
           }
         }

@@ -13,8 +13,9 @@
 
 namespace imd {
 
-// One GEMM launch: planes [plane0, plane0 + planes) of the residue buffers, K range
-// [k0, k0 + klen) of every row, into W planes starting at modulus mod0.
+// One GEMM launch: `planes` planes of the residue buffers, K range [k0, k0 + klen) of every row,
+// into the product planes starting at modulus mod0. A product plane holds
+// y = (q_l * sum_h RA RB) mod p_l, the form the CRT consumes.
 struct GemmShape {
   int32_t m, n_hat;        // rows of A per plane; padded rows of B per plane (= W row pitch)
   int32_t k_hat;           // row pitch of the residue planes (bytes)
@@ -24,8 +25,10 @@ struct GemmShape {
   int32_t mod0;            // first modulus of the group
   int32_t add;             // 0: W = acc mod p; 1: W = (W + acc) mod p
   uint32_t p[kMaxModuli];      // moduli of the group's slots (index = slot)
-  uint32_t magic[kMaxModuli];  // floor(2^32 / p)
-  uint32_t bias[kMaxModuli];   // the multiple of p in [2^31, 2^31 + p)
+  uint32_t magic[kMaxModuli];     // floor(2^32 / p): quotient within one of floor(v / p)
+  uint32_t magic_up[kMaxModuli];  // ceil(2^32 / p): exact quotient for v < 2^24
+  uint32_t bias[kMaxModuli];      // the multiple of p in [2^31, 2^31 + p)
+  uint32_t q[kMaxModuli];         // CRT weight inverse M_l^-1 mod p_l: the planes store q (A'B') mod p
 };
 
 struct GemmPlanInfo {

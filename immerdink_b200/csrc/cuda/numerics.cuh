@@ -108,100 +108,170 @@ __device__ __forceinline__ void quantize(uint64_t bits, int sigma, bool trunc, u
   *neg = (bits >> 63) != 0 && (*lo | *hi) != 0;
 }
 
-// Symmetric residue of +-|a'| for modulus index l: in [-floor(p/2), ceil(p/2) - 1].
+// Quantised value as a two's complement integer, fast path for N <= 16 (|a'| < 2^63): scale the
+// double by 2^sigma exactly (exponent add) and let the conversion unit round to nearest even (or
+// toward zero). Zeros, subnormals and non-finite inputs take the integer path.
+__device__ __forceinline__ int64_t quantize_i64(uint64_t bits, int sigma, bool trunc) {
+  const int ef = static_cast<int>((bits >> 52) & 0x7FF);
+  if (ef == 0 || ef == 0x7FF) {
+    uint64_t lo;
+    uint32_t hi;
+    bool neg;
+    quantize(bits, sigma, trunc, &lo, &hi, &neg);
+    return neg ? -static_cast<int64_t>(lo) : static_cast<int64_t>(lo);
+  }
+  const int en = ef + sigma;
+  if (en <= 0) return 0;  // |a 2^sigma| < 2^-1022
+  const uint64_t scaled = (bits & 0x800FFFFFFFFFFFFFull) | (static_cast<uint64_t>(en) << 52);
+  const double v = __longlong_as_double(static_cast<long long>(scaled));
+  return trunc ? __double2ll_rz(v) : __double2ll_rn(v);
+}
+
+// Signed base-256 digits of a two's complement integer: adding 0x80 to every byte but the top one
+// (with carries) and flipping those bits back turns each byte into a digit in [-128, 127].
+__device__ __forceinline__ void signed_digits64(int64_t x, uint32_t* d0, uint32_t* d1) {
+  const uint64_t k = 0x0080808080808080ull;
+  const uint64_t y = (static_cast<uint64_t>(x) + k) ^ k;
+  *d0 = static_cast<uint32_t>(y);
+  *d1 = static_cast<uint32_t>(y >> 32);
+}
+__device__ __forceinline__ void signed_digits96(uint64_t lo, uint32_t hi, bool neg, uint32_t* d0,
+                                                uint32_t* d1, uint32_t* d2) {
+  if (neg) {  // two's complement on 96 bits
+    lo = ~lo + 1;
+    hi = ~hi + (lo == 0 ? 1u : 0u);
+  }
+  const uint64_t k = 0x8080808080808080ull;
+  const uint64_t ylo = lo + k;
+  const uint32_t yhi = hi + 0x00808080u + (ylo < lo ? 1u : 0u);
+  *d0 = static_cast<uint32_t>(ylo ^ k);
+  *d1 = static_cast<uint32_t>((ylo ^ k) >> 32);
+  *d2 = yhi ^ 0x00808080u;
+}
+
+// Nonnegative residue u in [0, p) of the integer with signed digits (d0, d1, d2), modulus index l.
 template <int WORDS>
-__device__ __forceinline__ int residue(const ResidueTables& t, int l, uint32_t w0, uint32_t w1,
-                                       uint32_t w2, bool neg) {
-  uint32_t s = __dp4a(w0, t.weight[0][l], 0u);
-  s = __dp4a(w1, t.weight[1][l], s);
-  if (WORDS > 2) s = __dp4a(w2, t.weight[2][l], s);  // s <= 12 * 255^2 < 2^20
-  uint32_t v = neg ? t.lift[l] - s : s;              // >= 0, congruent to a'
-  v += t.half[l];
-  const uint32_t r = v - t.p[l] * __umulhi(v, t.magic[l]);  // v mod p, exact for v < 2^24
-  return static_cast<int>(r) - static_cast<int>(t.half[l]);
+__device__ __forceinline__ uint32_t residue_u(const ResidueTables& t, int l, uint32_t d0,
+                                              uint32_t d1, uint32_t d2) {
+  int s = __dp4a(static_cast<int>(d0), static_cast<int>(t.weight[0][l]), static_cast<int>(t.lift[l]));
+  s = __dp4a(static_cast<int>(d1), static_cast<int>(t.weight[1][l]), s);
+  if (WORDS > 2) s = __dp4a(static_cast<int>(d2), static_cast<int>(t.weight[2][l]), s);
+  const uint32_t v = static_cast<uint32_t>(s);  // 0 < v < 2^24
+  return v - t.p[l] * __umulhi(v, t.magic[l]);
+}
+
+// Four residues u (one per byte, each < p) -> four symmetric residues as two's complement bytes.
+__device__ __forceinline__ uint32_t symmetric4(const ResidueTables& t, int l, uint32_t packed) {
+  const uint32_t above = ((packed + t.fix_add[l]) >> 7) & 0x01010101u;  // 1 where u > ceil(p/2) - 1
+  return above * t.fix_mul[l] + packed;                                 // u + 256 - p there
 }
 
 // ---- CRT ------------------------------------------------------------------------------------
-// z = centred representative of the residues, as sign + magnitude on LIMBS 32-bit limbs.
-// S = sum_l M_l y_l (y_l = q_l W_l mod p_l) is not reduced on the way: S / P = sum y_l / p_l, so
-// the multiple of P to subtract is the rounding of a fixed-point estimate of that sum, followed
-// by one exact correction.
+// z = centred representative of the residues, as sign + magnitude on WORDS 32-bit words.
+// The product planes already hold y_l = (q_l W_l) mod p_l (the GEMM epilogue multiplies by q_l).
+// S = sum_l M_l y_l is accumulated on NL carry-free limbs (limb sums < 2^32), normalised once,
+// and not reduced on the way: the multiple of P to subtract is floor(x_lo + 1/2) for an
+// underestimate x_lo of S / P taken from the top 32 bits of S (within 2^-20), so that
+// S - q P lies in [-P/2, P/2 + P 2^-20) and one exact comparison with H finishes the centring.
+template <int NL>
+struct CrtShape {
+  static constexpr int kLw = NL <= 7 ? 20 : 19;
+  static constexpr int kWords = (NL * kLw + 31) / 32;
+};
+
 // Residue l is byte `lane` of packed[l].
-template <int LIMBS>
-__device__ __forceinline__ void crt(const CrtTables& t, const uint32_t* packed, int lane,
-                                    uint32_t* mag, bool* neg) {
-  uint32_t S[LIMBS];
+template <int NL, int LANE>
+__device__ __forceinline__ void crt(const CrtTables& t, const uint32_t* packed, uint32_t* mag,
+                                    bool* neg) {
+  constexpr int LW = CrtShape<NL>::kLw, WORDS = CrtShape<NL>::kWords;
+  uint32_t acc[NL];
 #pragma unroll
-  for (int i = 0; i < LIMBS; ++i) S[i] = 0;
-  uint32_t est = 0;  // sum y_l floor(2^26 / p_l): below the true sum by less than N 2^-18
+  for (int i = 0; i < NL; ++i) acc[i] = 0;
 #pragma unroll
   for (int l = 0; l < kMaxModuli; ++l) {
     if (l >= t.N) break;
-    const uint32_t v = t.q[l] * ((packed[l] >> (8 * lane)) & 0xFFu);
-    const uint32_t y = v - t.p[l] * __umulhi(v, t.magic[l]);
-    est += y * (t.frac[l] >> 1);
-    uint64_t c = 0;
+    const uint32_t y = (packed[l] >> (8 * LANE)) & 0xFFu;
 #pragma unroll
-    for (int i = 0; i < LIMBS; ++i) {
-      c += static_cast<uint64_t>(t.M[l][i]) * y + S[i];
-      S[i] = static_cast<uint32_t>(c);
-      c >>= 32;
-    }
+    for (int i = 0; i < NL; ++i) acc[i] += t.M[l][i] * y;
   }
-  const uint32_t q = (est + (1u << 25)) >> 26;
-  uint32_t Q[LIMBS];
+  // limbs -> 32-bit words
+  uint32_t S[WORDS];
   {
-    uint64_t c = 0;
+    uint64_t carry = 0;  // bits of the running sum at and above the current word
+    int word = 0;
 #pragma unroll
-    for (int i = 0; i < LIMBS; ++i) {
-      c += static_cast<uint64_t>(t.P[i]) * q;
-      Q[i] = static_cast<uint32_t>(c);
-      c >>= 32;
+    for (int i = 0; i < NL; ++i) {
+      const int off = i * LW - 32 * word;  // bit offset of limb i inside `carry` (0 <= off < 32)
+      carry += static_cast<uint64_t>(acc[i]) << off;
+      if ((i + 1) * LW >= 32 * (word + 1) || i == NL - 1) {
+        if (word < WORDS) S[word] = static_cast<uint32_t>(carry);
+        carry >>= 32;
+        ++word;
+      }
+    }
+#pragma unroll
+    for (int wd = word; wd < WORDS; ++wd) {
+      S[wd] = static_cast<uint32_t>(carry);
+      carry >>= 32;
     }
   }
-  // d = S - Q (two's complement); negative iff S < Q
-  int64_t b = 0;
-  uint32_t d[LIMBS];
+  // multiple of P
+  uint32_t top;
+  {
+    const int w = t.qshift >> 5, sh = t.qshift & 31;
+    uint32_t lo = 0, hi = 0;
 #pragma unroll
-  for (int i = 0; i < LIMBS; ++i) {
-    b += static_cast<int64_t>(S[i]) - static_cast<int64_t>(Q[i]);
-    d[i] = static_cast<uint32_t>(b);
-    b >>= 32;
+    for (int i = 0; i < WORDS; ++i) {
+      if (i == w) lo = S[i];
+      if (i == w + 1) hi = S[i];
+    }
+    top = __funnelshift_r(lo, hi, sh);
   }
-  bool ng = b < 0;
-  if (ng) {  // magnitude = -d
+  const uint32_t q = (__umulhi(top, t.rinv) + (1u << (t.rshift - 1))) >> t.rshift;
+  // d = S - q P (two's complement on WORDS words)
+  uint32_t d[WORDS];
+  {
+    uint64_t mul = 0;
+    int64_t bor = 0;
+#pragma unroll
+    for (int i = 0; i < WORDS; ++i) {
+      mul += static_cast<uint64_t>(t.P[i]) * q;
+      bor += static_cast<int64_t>(S[i]) - static_cast<int64_t>(static_cast<uint32_t>(mul));
+      d[i] = static_cast<uint32_t>(bor);
+      bor >>= 32;
+      mul >>= 32;
+    }
+    *neg = bor < 0;
+  }
+  if (*neg) {  // magnitude = -d
     uint64_t c = 1;
 #pragma unroll
-    for (int i = 0; i < LIMBS; ++i) {
+    for (int i = 0; i < WORDS; ++i) {
       c += static_cast<uint32_t>(~d[i]);
       d[i] = static_cast<uint32_t>(c);
       c >>= 32;
     }
   } else {
-    // d in [0, P/2 + small): if d > H the representative is d - P
-    bool gt = false, decided = false;
+    // d in [0, P/2 + small): if d > H the representative is d - P, of magnitude P - d
+    int64_t bb = 0;  // sign of H - d
 #pragma unroll
-    for (int i = LIMBS - 1; i >= 0; --i) {
-      const uint32_t hv = i < kCrtLimbs ? t.H[i] : 0u;
-      if (!decided && d[i] != hv) {
-        gt = d[i] > hv;
-        decided = true;
-      }
+    for (int i = 0; i < WORDS; ++i) {
+      bb += static_cast<int64_t>(t.H[i]) - static_cast<int64_t>(d[i]);
+      bb >>= 32;
     }
-    if (gt) {
-      int64_t bb = 0;
+    if (bb < 0) {
+      int64_t b2 = 0;
 #pragma unroll
-      for (int i = 0; i < LIMBS; ++i) {
-        bb += static_cast<int64_t>(t.P[i]) - static_cast<int64_t>(d[i]);
-        d[i] = static_cast<uint32_t>(bb);
-        bb >>= 32;
+      for (int i = 0; i < WORDS; ++i) {
+        b2 += static_cast<int64_t>(t.P[i]) - static_cast<int64_t>(d[i]);
+        d[i] = static_cast<uint32_t>(b2);
+        b2 >>= 32;
       }
-      ng = true;
+      *neg = true;
     }
   }
 #pragma unroll
-  for (int i = 0; i < LIMBS; ++i) mag[i] = d[i];
-  *neg = ng;
+  for (int i = 0; i < WORDS; ++i) mag[i] = d[i];
 }
 
 // 64 bits of mag starting at bit position pos (pos >= 0).
@@ -269,6 +339,36 @@ __device__ __forceinline__ double round_scaled(const uint32_t* mag, bool neg, in
   if (rb == 53) out = (static_cast<uint64_t>(q + 1075) << 52) | (r & 0xFFFFFFFFFFFFFull);
   else out = r;  // subnormal: q == -1074
   return __longlong_as_double(static_cast<long long>(sign | out));
+}
+
+// The same value by the conversion unit when the result is a normal number: the top 64 bits of the
+// magnitude, with every lower bit folded into a sticky last bit, are rounded once by the u64 ->
+// f64 conversion (64 bits leave 11 guard bits, so the sticky bit cannot change a tie into a
+// non-tie wrongly), and the power of two is an exponent add. Subnormal and overflowing results
+// take round_scaled.
+template <int LIMBS>
+__device__ __forceinline__ double round_scaled_fast(const uint32_t* mag, bool neg, int e) {
+  int bl = 0;
+#pragma unroll
+  for (int i = 0; i < LIMBS; ++i)
+    if (mag[i]) bl = 32 * i + 32 - __clz(static_cast<int>(mag[i]));
+  if (bl == 0) return 0.0;
+  const int pos = bl - 64;
+  uint64_t top;
+  if (LIMBS <= 2 || pos <= 0) {
+    top = bits_at<LIMBS>(mag, 0) << (-pos);          // bl <= 64: everything fits, exact
+  } else {
+    top = bits_at<LIMBS>(mag, pos);
+    if (any_below<LIMBS>(mag, pos)) top |= 1;
+  }
+  const double v = __ull2double_rn(top);              // in [2^63, 2^64]
+  const long long vb = __double_as_longlong(v);
+  const int ex = static_cast<int>(vb >> 52) + pos + e;  // biased exponent of the result
+  if (ex >= 1 && ex <= 2046) {
+    const long long out = vb + (static_cast<long long>(pos + e) << 52);
+    return __longlong_as_double(neg ? (out | static_cast<long long>(0x8000000000000000ull)) : out);
+  }
+  return round_scaled<LIMBS>(mag, neg, e);
 }
 
 }  // namespace dev

@@ -180,6 +180,7 @@ struct ResidueParams {
   const int64_t *row, *kv, *bat;
   int64_t rows, rows_pad, batches, k, k_hat;
   int32_t rows_fast;
+  int32_t lg_fast;     // log2 of the threads of a CTA that run along the fast direction
   int32_t trunc;
   int32_t mod0, mods;  // first modulus and number of moduli of the group
   const int16_t* sigma;
@@ -187,56 +188,63 @@ struct ResidueParams {
   ResidueTables t;
 };
 
+// Grid: x covers the fast direction of the operand (K chunks when K is contiguous, rows when the
+// rows are) with 2^lg_fast threads of each CTA, y (and the remaining threads) stride over the other
+// one, so no thread divides a 64-bit index.
 template <int WORDS>
 __global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ ResidueParams p) {
   const int64_t chunks = p.k_hat >> 4;
   const int64_t total_rows = p.rows_pad * p.batches;
-  const int64_t item = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (item >= total_rows * chunks) return;
-  int64_t rho, c;
-  if (p.rows_fast) {
-    rho = item % total_rows;
-    c = item / total_rows;
-  } else {
-    c = item % chunks;
-    rho = item / chunks;
-  }
-  const int64_t lam = rho / p.rows_pad, i = rho % p.rows_pad;
-  const bool live = i < p.rows;
-  uint32_t w0[16], w1[16], w2[16];
-  uint32_t negmask = 0;
-  const int64_t h0 = c << 4;
-  if (live) {
-    const double* base = p.X + p.bat[lam] + p.row[i];
-    const int sg = p.sigma[lam * p.rows + i];
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      uint64_t lo = 0;
-      uint32_t hi = 0;
-      bool neg = false;
-      if (h0 + e < p.k) {
-        const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h0 + e]]));
-        dev::quantize(u, sg, p.trunc != 0, &lo, &hi, &neg);
-      }
-      w0[e] = static_cast<uint32_t>(lo);
-      w1[e] = static_cast<uint32_t>(lo >> 32);
-      w2[e] = hi;
-      negmask |= (neg ? 1u : 0u) << e;
-    }
-  }
-  int8_t* out = p.R + (lam * p.rows_pad + i) * p.k_hat + h0;
+  const int F = 1 << p.lg_fast, per = kThreads >> p.lg_fast;
+  const int64_t fast = static_cast<int64_t>(blockIdx.x) * F + (threadIdx.x & (F - 1));
+  const int64_t fast_n = p.rows_fast ? total_rows : chunks;
+  const int64_t slow_n = p.rows_fast ? chunks : total_rows;
+  if (fast >= fast_n) return;
   const int64_t plane = p.batches * p.rows_pad * p.k_hat;
-  for (int s = 0; s < p.mods; ++s) {
-    uint32_t pk[4] = {0, 0, 0, 0};
+  for (int64_t slow = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
+       slow < slow_n; slow += static_cast<int64_t>(gridDim.y) * per) {
+    const int64_t rho = p.rows_fast ? fast : slow;
+    const int64_t c = p.rows_fast ? slow : fast;
+    int64_t lam = 0, i = rho;
+    if (p.batches != 1) {
+      lam = rho / p.rows_pad;
+      i = rho - lam * p.rows_pad;
+    }
+    const bool live = i < p.rows;
+    uint32_t d0[16], d1[16], d2[16];
+    const int64_t h0 = c << 4;
     if (live) {
-      const int l = p.mod0 + s;
+      const double* base = p.X + p.bat[lam] + p.row[i];
+      const int sg = p.sigma[lam * p.rows + i];
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
-        const int r = dev::residue<WORDS>(p.t, l, w0[e], w1[e], w2[e], (negmask >> e) & 1);
-        pk[e >> 2] |= (static_cast<uint32_t>(r) & 0xFFu) << (8 * (e & 3));
+        uint64_t u = 0;
+        if (h0 + e < p.k) u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h0 + e]]));
+        if (WORDS == 2) {
+          dev::signed_digits64(dev::quantize_i64(u, sg, p.trunc != 0), &d0[e], &d1[e]);
+          d2[e] = 0;
+        } else {
+          uint64_t lo;
+          uint32_t hi;
+          bool neg;
+          dev::quantize(u, sg, p.trunc != 0, &lo, &hi, &neg);
+          dev::signed_digits96(lo, hi, neg, &d0[e], &d1[e], &d2[e]);
+        }
       }
     }
-    *reinterpret_cast<uint4*>(out + s * plane) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    int8_t* out = p.R + (lam * p.rows_pad + i) * p.k_hat + h0;
+    for (int s = 0; s < p.mods; ++s) {
+      uint32_t pk[4] = {0, 0, 0, 0};
+      if (live) {
+        const int l = p.mod0 + s;
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          pk[e >> 2] |= dev::residue_u<WORDS>(p.t, l, d0[e], d1[e], d2[e]) << (8 * (e & 3));
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) pk[wd] = dev::symmetric4(p.t, l, pk[wd]);
+      }
+      *reinterpret_cast<uint4*>(out + s * plane) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
   }
 }
 
@@ -249,6 +257,7 @@ struct CrtParams {
   double* C;
   Vectors v;
   int64_t m, n, n_hat, k, b;
+  int32_t lg_fast;
   double alpha, beta;
   CrtTables t;
 };
@@ -265,41 +274,77 @@ __device__ __noinline__ double native_dot(const double* a, const double* b, cons
   return acc;
 }
 
-// One thread = 4 consecutive columns of one row of one batch.
-template <int LIMBS>
+// One output of the thread's four: flagged rows / columns take the native FMA chain.
+template <int NL, int LANE>
+__device__ __forceinline__ double crt_value(const CrtParams& p, const uint32_t* packed, int64_t lam,
+                                            int64_t i, int64_t j, int si, bool fa, int tau, bool fb) {
+  constexpr int WORDS = dev::CrtShape<NL>::kWords;
+  if (fa || fb)
+    return native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j],
+                      p.v.a_k, p.v.b_k, p.k);
+  uint32_t mag[WORDS];
+  bool neg;
+  dev::crt<NL, LANE>(p.t, packed, mag, &neg);
+  return dev::round_scaled_fast<WORDS>(mag, neg, -(si + tau));
+}
+
+// One thread = 4 consecutive columns of one row of one batch. Grid: x (with 2^lg_fast threads of a
+// CTA) covers the column quads of a row, y and the remaining threads stride over the rows.
+template <int NL>
 __global__ void __launch_bounds__(kThreads) k_crt(const __grid_constant__ CrtParams p) {
   const int64_t quads = p.n_hat >> 2;
-  const int64_t item = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (item >= p.b * p.m * quads) return;
-  const int64_t jq = item % quads, rho = item / quads;
-  const int64_t lam = rho / p.m, i = rho % p.m;
+  const int F = 1 << p.lg_fast, per = kThreads >> p.lg_fast;
+  const int64_t jq = static_cast<int64_t>(blockIdx.x) * F + (threadIdx.x & (F - 1));
   const int64_t j0 = jq << 2;
-  if (j0 >= p.n) return;
+  if (jq >= quads || j0 >= p.n) return;
   const int64_t plane = p.b * p.m * p.n_hat;
-  const uint8_t* w = p.W + (lam * p.m + i) * p.n_hat + j0;
-  uint32_t packed[kMaxModuli];
-#pragma unroll
-  for (int l = 0; l < kMaxModuli; ++l)
-    packed[l] = l < p.t.N ? *reinterpret_cast<const uint32_t*>(w + l * plane) : 0u;
-  const int si = p.sigma[lam * p.m + i];
-  const bool fa = p.fA[lam * p.m + i] != 0;
-  double* crow = p.C + p.v.c_bat[lam] + p.v.c_row[i];
-#pragma unroll 1
-  for (int e = 0; e < 4; ++e) {
-    const int64_t j = j0 + e;
-    if (j >= p.n) break;
-    double D;
-    if (fa || p.fB[lam * p.n + j] != 0) {
-      D = native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j],
-                     p.v.a_k, p.v.b_k, p.k);
-    } else {
-      uint32_t mag[LIMBS];
-      bool neg;
-      dev::crt<LIMBS>(p.t, packed, e, mag, &neg);
-      D = dev::round_scaled<LIMBS>(mag, neg, -(si + static_cast<int>(p.tau[lam * p.n + j])));
+  const int64_t total_rows = p.b * p.m;
+  for (int64_t rho = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
+       rho < total_rows; rho += static_cast<int64_t>(gridDim.y) * per) {
+    int64_t lam = 0, i = rho;
+    if (p.b != 1) {
+      lam = rho / p.m;
+      i = rho - lam * p.m;
     }
-    double* c = crow + p.v.c_col[j];
-    *c = finish(D, p.alpha, p.beta, c);
+    const uint8_t* w = p.W + rho * p.n_hat + j0;
+    uint32_t packed[kMaxModuli];
+#pragma unroll
+    for (int l = 0; l < kMaxModuli; ++l)
+      packed[l] = l < p.t.N ? *reinterpret_cast<const uint32_t*>(w + l * plane) : 0u;
+    const int si = p.sigma[rho];
+    const bool fa = p.fA[rho] != 0;
+    const int16_t* tau = p.tau + lam * p.n + j0;
+    const uint8_t* fb = p.fB + lam * p.n + j0;
+    const int64_t left = p.n - j0;  // >= 1
+    double D[4];
+    D[0] = crt_value<NL, 0>(p, packed, lam, i, j0, si, fa, tau[0], fb[0] != 0);
+    D[1] = left > 1 ? crt_value<NL, 1>(p, packed, lam, i, j0 + 1, si, fa, tau[1], fb[1] != 0) : 0.0;
+    D[2] = left > 2 ? crt_value<NL, 2>(p, packed, lam, i, j0 + 2, si, fa, tau[2], fb[2] != 0) : 0.0;
+    D[3] = left > 3 ? crt_value<NL, 3>(p, packed, lam, i, j0 + 3, si, fa, tau[3], fb[3] != 0) : 0.0;
+    double* crow = p.C + p.v.c_bat[lam] + p.v.c_row[i];
+    const int64_t c0 = p.v.c_col[j0];
+    double* c = crow + c0;
+    // four adjacent, 32-byte aligned outputs go out as two 16-byte stores
+    if (left > 3 && p.v.c_col[j0 + 3] == c0 + 3 && p.v.c_col[j0 + 1] == c0 + 1 &&
+        p.v.c_col[j0 + 2] == c0 + 2 && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+      double2* c2 = reinterpret_cast<double2*>(c);
+      double2 lo, hi;
+      if (p.beta != 0.0) {
+        lo = c2[0];
+        hi = c2[1];
+      }
+      lo.x = finish(D[0], p.alpha, p.beta, &lo.x);
+      lo.y = finish(D[1], p.alpha, p.beta, &lo.y);
+      hi.x = finish(D[2], p.alpha, p.beta, &hi.x);
+      hi.y = finish(D[3], p.alpha, p.beta, &hi.y);
+      c2[0] = lo;
+      c2[1] = hi;
+    } else {
+      for (int e = 0; e < 4 && e < left; ++e) {
+        double* ce = crow + p.v.c_col[j0 + e];
+        *ce = finish(D[e], p.alpha, p.beta, ce);
+      }
+    }
   }
 }
 
@@ -351,10 +396,10 @@ __global__ void __launch_bounds__(kThreads) k_gemm_reference(const __grid_consta
   for (int h = 0; h < s.klen; h += 4)
     acc = __dp4a(*reinterpret_cast<const int*>(a + h), *reinterpret_cast<const int*>(b + h), acc);
   uint8_t* w = W + ((static_cast<int64_t>(s.mod0 + slot) * s.batches + z % s.batches) * s.m + i) * s.n_hat + j;
-  const int64_t v = static_cast<int64_t>(acc) + (s.add ? *w : 0);
   const int64_t pm = s.p[slot];
-  int64_t r = v % pm;
+  int64_t r = static_cast<int64_t>(acc) % pm;
   if (r < 0) r += pm;
+  r = (r * s.q[slot] + (s.add ? *w : 0)) % pm;  // planes hold y = q (A'B') mod p
   *w = static_cast<uint8_t>(r);
 }
 
@@ -399,7 +444,7 @@ imd_status_t gemm_reference_launch(const GemmShape& s, const int8_t* RA, const i
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
 
-GemmShape gemm_shape(const ExecPlan& e, int mod0, int mods, int chunk) {
+GemmShape gemm_shape(const ExecPlan& e, const uint32_t* crt_q, int mod0, int mods, int chunk) {
   GemmShape s{};
   s.m = static_cast<int32_t>(e.m);
   s.n_hat = static_cast<int32_t>(e.n_hat);
@@ -414,7 +459,9 @@ GemmShape gemm_shape(const ExecPlan& e, int mod0, int mods, int chunk) {
     const uint32_t p = static_cast<uint32_t>(kModuli[mod0 + i]);
     s.p[i] = p;
     s.magic[i] = static_cast<uint32_t>((uint64_t{1} << 32) / p);
+    s.magic_up[i] = static_cast<uint32_t>(((uint64_t{1} << 32) + p - 1) / p);
     s.bias[i] = static_cast<uint32_t>(((uint64_t{1} << 31) + p - 1) / p * p);
+    s.q[i] = crt_q[mod0 + i];
   }
   return s;
 }
@@ -549,14 +596,21 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
       p.sigma = x == 0 ? sA : sB;
       p.R = x == 0 ? RA : RB;
       p.t = rt;
-      const unsigned int grid = grid_for(p.rows_pad * p.batches * (p.k_hat >> 4));
+      const int64_t fast_n = p.rows_fast ? p.rows_pad * p.batches : (p.k_hat >> 4);
+      const int64_t slow_n = p.rows_fast ? (p.k_hat >> 4) : p.rows_pad * p.batches;
+      p.lg_fast = 0;
+      while (p.lg_fast < 8 && (int64_t{1} << p.lg_fast) < fast_n) ++p.lg_fast;
+      const int64_t F = int64_t{1} << p.lg_fast, per = kThreads / F;
+      const int64_t gy = (slow_n + per - 1) / per;
+      const dim3 grid(static_cast<unsigned int>((fast_n + F - 1) / F),
+                      static_cast<unsigned int>(gy < 65535 ? gy : 65535));
       if (rt.words == 2) k_residues<2><<<grid, kThreads, 0, stream>>>(p);
       else k_residues<3><<<grid, kThreads, 0, stream>>>(p);
       if (!launched()) return IMD_STATUS_CUDA_ERROR;
     }
     mark(2, stream);
     for (int64_t c = 0; c < e.k_chunks; ++c) {
-      const GemmShape s = gemm_shape(e, g0, mods, static_cast<int>(c));
+      const GemmShape s = gemm_shape(e, plan.crt.q, g0, mods, static_cast<int>(c));
       const imd_status_t st = use_reference_gemm() ? gemm_reference_launch(s, RA, RB, W, stream)
                                                    : gemm_launch(info, s, RA, RB, W, stream);
       if (st != IMD_STATUS_SUCCESS) return st;
@@ -572,13 +626,23 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   p.m = e.m, p.n = e.n, p.n_hat = e.n_hat, p.k = e.k, p.b = e.b;
   p.alpha = alpha, p.beta = beta;
   p.t = plan.crt;
-  const unsigned int grid = grid_for(e.b * e.m * (e.n_hat >> 2));
-  switch (plan.crt.limbs) {
+  const int64_t quads = e.n_hat >> 2, rows_total = e.b * e.m;
+  p.lg_fast = 0;
+  while (p.lg_fast < 8 && (int64_t{1} << p.lg_fast) < quads) ++p.lg_fast;
+  const int64_t Fq = int64_t{1} << p.lg_fast, perq = kThreads / Fq;
+  const int64_t gyq = (rows_total + perq - 1) / perq;
+  const dim3 grid(static_cast<unsigned int>((quads + Fq - 1) / Fq),
+                  static_cast<unsigned int>(gyq < 65535 ? gyq : 65535));
+  switch (plan.crt.nl) {
     case 1: k_crt<1><<<grid, kThreads, 0, stream>>>(p); break;
     case 2: k_crt<2><<<grid, kThreads, 0, stream>>>(p); break;
     case 3: k_crt<3><<<grid, kThreads, 0, stream>>>(p); break;
     case 4: k_crt<4><<<grid, kThreads, 0, stream>>>(p); break;
-    default: k_crt<5><<<grid, kThreads, 0, stream>>>(p); break;
+    case 5: k_crt<5><<<grid, kThreads, 0, stream>>>(p); break;
+    case 6: k_crt<6><<<grid, kThreads, 0, stream>>>(p); break;
+    case 7: k_crt<7><<<grid, kThreads, 0, stream>>>(p); break;
+    case 8: k_crt<8><<<grid, kThreads, 0, stream>>>(p); break;
+    default: k_crt<9><<<grid, kThreads, 0, stream>>>(p); break;
   }
   mark(4, stream);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;

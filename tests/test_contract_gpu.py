@@ -53,8 +53,11 @@ def test_golden_matrix(case, reference_gemm):
         assert np.array_equal(RA[:, :, :k], g["RA"]) and not RA[:, :, k:].any()
         assert np.array_equal(RB[:, :nn, :k], g["RB"])
         assert not RB[:, nn:, :].any() and not RB[:, :, k:].any()
+        # the product planes hold the CRT digits y_l = (q_l W_l) mod p_l
         W = ws.region(lay["W"][0], N * mm * nh, np.uint8).reshape(N, mm, nh)
-        assert np.array_equal(W[:, :, :nn], g["W"])
+        q = np.array(orc.constants(N)[4], np.int64)[:, None, None]
+        pm = np.array(orc.MODULI[:N], np.int64)[:, None, None]
+        assert np.array_equal(W[:, :, :nn], (g["W"].astype(np.int64) * q) % pm)
     plan.close()
 
 
