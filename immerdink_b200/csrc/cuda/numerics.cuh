@@ -8,6 +8,7 @@
 #pragma once
 #include <cstdint>
 
+#include "carry.cuh"
 #include "common/wide.hpp"
 #include "kernels.hpp"
 
@@ -173,23 +174,27 @@ __device__ __forceinline__ uint32_t symmetric4(const ResidueTables& t, int l, ui
 // and not reduced on the way: the multiple of P to subtract is floor(x_lo + 1/2) for an
 // underestimate x_lo of S / P taken from the top 32 bits of S (within 2^-20), so that
 // S - q P lies in [-P/2, P/2 + P 2^-20) and one exact comparison with H finishes the centring.
-template <int NL>
+// Limbs of the unreduced sum per N (20-bit limbs up to N = 16, 19-bit above): ceil(bitlen(N P) / lw).
+__host__ __device__ constexpr int crt_limbs_of(int N) {
+  constexpr int t[21] = {0, 0, 1, 2, 2, 3, 3, 3, 4, 4, 5, 5, 5, 6, 6, 7, 7, 8, 8, 9, 9};
+  return t[N];
+}
+template <int N>
 struct CrtShape {
-  static constexpr int kLw = NL <= 7 ? 20 : 19;
-  static constexpr int kWords = (NL * kLw + 31) / 32;
+  static constexpr int kNl = crt_limbs_of(N);
+  static constexpr int kLw = N <= 16 ? 20 : 19;
+  static constexpr int kWords = (kNl * kLw + 31) / 32;
 };
 
-// Residue l is byte `lane` of packed[l].
-template <int NL, int LANE>
-__device__ __forceinline__ void crt(const CrtTables& t, const uint32_t* packed, uint32_t* mag,
-                                    bool* neg) {
-  constexpr int LW = CrtShape<NL>::kLw, WORDS = CrtShape<NL>::kWords;
+// Residue l is byte LANE of packed[l]. Returns the magnitude of z in mag[] and its sign.
+template <int N, int LANE>
+__device__ __forceinline__ bool crt(const CrtTables& t, const uint32_t* packed, uint32_t* mag) {
+  constexpr int NL = CrtShape<N>::kNl, LW = CrtShape<N>::kLw, WORDS = CrtShape<N>::kWords;
   uint32_t acc[NL];
 #pragma unroll
   for (int i = 0; i < NL; ++i) acc[i] = 0;
 #pragma unroll
-  for (int l = 0; l < kMaxModuli; ++l) {
-    if (l >= t.N) break;
+  for (int l = 0; l < N; ++l) {
     const uint32_t y = (packed[l] >> (8 * LANE)) & 0xFFu;
 #pragma unroll
     for (int i = 0; i < NL; ++i) acc[i] += t.M[l][i] * y;
@@ -215,7 +220,7 @@ __device__ __forceinline__ void crt(const CrtTables& t, const uint32_t* packed, 
       carry >>= 32;
     }
   }
-  // multiple of P
+  // multiple of P to subtract
   uint32_t top;
   {
     const int w = t.qshift >> 5, sh = t.qshift & 31;
@@ -228,50 +233,38 @@ __device__ __forceinline__ void crt(const CrtTables& t, const uint32_t* packed, 
     top = __funnelshift_r(lo, hi, sh);
   }
   const uint32_t q = (__umulhi(top, t.rinv) + (1u << (t.rshift - 1))) >> t.rshift;
-  // d = S - q P (two's complement on WORDS words)
-  uint32_t d[WORDS];
+  uint32_t Q[WORDS];
   {
     uint64_t mul = 0;
-    int64_t bor = 0;
 #pragma unroll
     for (int i = 0; i < WORDS; ++i) {
       mul += static_cast<uint64_t>(t.P[i]) * q;
-      bor += static_cast<int64_t>(S[i]) - static_cast<int64_t>(static_cast<uint32_t>(mul));
-      d[i] = static_cast<uint32_t>(bor);
-      bor >>= 32;
+      Q[i] = static_cast<uint32_t>(mul);
       mul >>= 32;
     }
-    *neg = bor < 0;
   }
-  if (*neg) {  // magnitude = -d
-    uint64_t c = 1;
+  uint32_t d1[WORDS], d2[WORDS];
+  const uint32_t below = Words<WORDS>::sub(d1, S, Q);  // S - Q
+  Words<WORDS>::sub(d2, Q, S);                         // Q - S
 #pragma unroll
-    for (int i = 0; i < WORDS; ++i) {
-      c += static_cast<uint32_t>(~d[i]);
-      d[i] = static_cast<uint32_t>(c);
-      c >>= 32;
-    }
-  } else {
-    // d in [0, P/2 + small): if d > H the representative is d - P, of magnitude P - d
-    int64_t bb = 0;  // sign of H - d
+  for (int i = 0; i < WORDS; ++i) mag[i] = below ? d2[i] : d1[i];
+  bool neg = below != 0;
+  if (!neg) {
+    // S - Q in [0, P/2 + P 2^-20): above H only at the very edge of the range
+    uint32_t tmp[WORDS], Hw[WORDS];
 #pragma unroll
-    for (int i = 0; i < WORDS; ++i) {
-      bb += static_cast<int64_t>(t.H[i]) - static_cast<int64_t>(d[i]);
-      bb >>= 32;
-    }
-    if (bb < 0) {
-      int64_t b2 = 0;
+    for (int i = 0; i < WORDS; ++i) Hw[i] = t.H[i];
+    if (Words<WORDS>::sub(tmp, Hw, mag)) {
+      uint32_t Pw[WORDS];
 #pragma unroll
-      for (int i = 0; i < WORDS; ++i) {
-        b2 += static_cast<int64_t>(t.P[i]) - static_cast<int64_t>(d[i]);
-        d[i] = static_cast<uint32_t>(b2);
-        b2 >>= 32;
-      }
-      *neg = true;
+      for (int i = 0; i < WORDS; ++i) Pw[i] = t.P[i];
+      Words<WORDS>::sub(tmp, Pw, mag);
+#pragma unroll
+      for (int i = 0; i < WORDS; ++i) mag[i] = tmp[i];
+      neg = true;
     }
   }
-#pragma unroll
-  for (int i = 0; i < WORDS; ++i) mag[i] = d[i];
+  return neg;
 }
 
 // 64 bits of mag starting at bit position pos (pos >= 0).
@@ -341,34 +334,56 @@ __device__ __forceinline__ double round_scaled(const uint32_t* mag, bool neg, in
   return __longlong_as_double(static_cast<long long>(sign | out));
 }
 
-// The same value by the conversion unit when the result is a normal number: the top 64 bits of the
-// magnitude, with every lower bit folded into a sticky last bit, are rounded once by the u64 ->
-// f64 conversion (64 bits leave 11 guard bits, so the sticky bit cannot change a tie into a
-// non-tie wrongly), and the power of two is an exponent add. Subnormal and overflowing results
-// take round_scaled.
+// The same value by the conversion unit when the result is a normal number: the magnitude is
+// shifted left until its leading bit is bit 32 LIMBS - 1; the top 64 bits, with every lower bit
+// folded into a sticky last bit, are rounded once by the u64 -> f64 conversion (64 bits leave 11
+// guard bits, so the sticky bit decides ties correctly), and the power of two is an exponent add.
+// Zero, subnormal and overflowing results take the exact integer path.
+template <int LIMBS>
+__device__ __noinline__ double round_scaled_slow(const uint32_t* mag, bool neg, int e) {
+  return round_scaled<LIMBS>(mag, neg, e);
+}
+
 template <int LIMBS>
 __device__ __forceinline__ double round_scaled_fast(const uint32_t* mag, bool neg, int e) {
-  int bl = 0;
+  uint32_t w[LIMBS];
 #pragma unroll
-  for (int i = 0; i < LIMBS; ++i)
-    if (mag[i]) bl = 32 * i + 32 - __clz(static_cast<int>(mag[i]));
-  if (bl == 0) return 0.0;
-  const int pos = bl - 64;
-  uint64_t top;
-  if (LIMBS <= 2 || pos <= 0) {
-    top = bits_at<LIMBS>(mag, 0) << (-pos);          // bl <= 64: everything fits, exact
-  } else {
-    top = bits_at<LIMBS>(mag, pos);
-    if (any_below<LIMBS>(mag, pos)) top |= 1;
+  for (int i = 0; i < LIMBS; ++i) w[i] = mag[i];
+  int lz = 0;  // leading zero bits of the LIMBS-word number
+  // whole words first (static cascade), then bits
+#pragma unroll
+  for (int step = 0; step < LIMBS - 1; ++step) {
+    if (w[LIMBS - 1] == 0) {
+#pragma unroll
+      for (int i = LIMBS - 1; i > 0; --i) w[i] = w[i - 1];
+      w[0] = 0;
+      lz += 32;
+    }
   }
-  const double v = __ull2double_rn(top);              // in [2^63, 2^64]
+  if (w[LIMBS - 1] == 0) return 0.0;
+  const int s = __clz(static_cast<int>(w[LIMBS - 1]));
+  lz += s;
+  uint32_t hi, mid, rest = 0;
+  if (LIMBS == 1) {
+    hi = w[0] << s;
+    mid = 0;
+  } else {
+    hi = __funnelshift_l(w[LIMBS - 2], w[LIMBS - 1], s);
+    mid = __funnelshift_l(LIMBS > 2 ? w[LIMBS - 3] : 0u, w[LIMBS - 2], s);
+    if (LIMBS > 2) rest = w[LIMBS - 3] << s;
+#pragma unroll
+    for (int i = 0; i < LIMBS - 3; ++i) rest |= w[i];
+  }
+  const uint64_t top = (static_cast<uint64_t>(hi) << 32) | mid | (rest != 0 ? 1u : 0u);
+  const double v = __ull2double_rn(top);                    // in [2^63, 2^64]
   const long long vb = __double_as_longlong(v);
-  const int ex = static_cast<int>(vb >> 52) + pos + e;  // biased exponent of the result
+  const int shift = 32 * LIMBS - 64 - lz + e;               // value = v 2^shift
+  const int ex = static_cast<int>(vb >> 52) + shift;        // biased exponent of the result
   if (ex >= 1 && ex <= 2046) {
-    const long long out = vb + (static_cast<long long>(pos + e) << 52);
+    const long long out = vb + (static_cast<long long>(shift) << 52);
     return __longlong_as_double(neg ? (out | static_cast<long long>(0x8000000000000000ull)) : out);
   }
-  return round_scaled<LIMBS>(mag, neg, e);
+  return round_scaled_slow<LIMBS>(mag, neg, e);
 }
 
 }  // namespace dev

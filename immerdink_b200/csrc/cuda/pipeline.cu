@@ -114,13 +114,27 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
   // (0 = no finite nonzero entry).
   int g = 0;
   if (live)
-    for (int64_t h = kl; h < p.k; h += KT) {
-      const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h]]));
-      uint64_t M;
-      int E;
-      const int c = dev::decompose(u, &M, &E);
-      if (c < 0) g |= 1 << 30;
-      else if (c > 0) g = (g & (1 << 30)) | max(g & 0xFFFF, E + 52 + 2048);
+    for (int64_t h = kl; h < p.k; h += 4 * KT) {
+      uint64_t u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {  // four independent loads in flight
+        const int64_t hj = h + static_cast<int64_t>(j) * KT;
+        u[j] = hj < p.k ? static_cast<uint64_t>(__double_as_longlong(base[p.kv[hj]])) : 0ull;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int ef = static_cast<int>(u[j] >> 52) & 0x7FF;
+        if (ef == 0x7FF) {
+          g |= 1 << 30;
+        } else if (ef != 0) {
+          g = (g & (1 << 30)) | max(g & 0xFFFF, ef + 1025);  // E + 52 + 2048 with E = ef - 1075
+        } else if ((u[j] << 1) != 0) {                       // subnormal: true exponent
+          uint64_t M;
+          int E;
+          dev::decompose(u[j], &M, &E);
+          g = (g & (1 << 30)) | max(g & 0xFFFF, E + 52 + 2048);
+        }
+      }
     }
   const int slot = r * KT + kl;
   s_gamma[slot] = g;
@@ -139,15 +153,23 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
   // pass 2: S = sum ceil(x^2 2^60), exact in 128 bits, order-independent
   uint64_t hi = 0, lo = 0;
   if (live && any)
-    for (int64_t h = kl; h < p.k; h += KT) {
-      const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h]]));
-      uint64_t M;
-      int E;
-      if (dev::decompose(u, &M, &E) == 1) {
-        uint64_t th, tl;
-        dev::square_term(M, E, gamma, &th, &tl);
-        lo += tl;
-        hi += th + (lo < tl ? 1 : 0);
+    for (int64_t h = kl; h < p.k; h += 4 * KT) {
+      uint64_t u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int64_t hj = h + static_cast<int64_t>(j) * KT;
+        u[j] = hj < p.k ? static_cast<uint64_t>(__double_as_longlong(base[p.kv[hj]])) : 0ull;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint64_t M;
+        int E;
+        if (dev::decompose(u[j], &M, &E) == 1) {
+          uint64_t th, tl;
+          dev::square_term(M, E, gamma, &th, &tl);
+          lo += tl;
+          hi += th + (lo < tl ? 1 : 0);
+        }
       }
     }
   s_hi[slot] = hi;
@@ -179,6 +201,7 @@ struct ResidueParams {
   const double* X;
   const int64_t *row, *kv, *bat;
   int64_t rows, rows_pad, batches, k, k_hat;
+  int64_t k_run;       // length of the runs of K positions that are adjacent in memory (0: none)
   int32_t rows_fast;
   int32_t lg_fast;     // log2 of the threads of a CTA that run along the fast direction
   int32_t trunc;
@@ -216,18 +239,45 @@ __global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ R
     if (live) {
       const double* base = p.X + p.bat[lam] + p.row[i];
       const int sg = p.sigma[lam * p.rows + i];
+      // all sixteen loads are issued before anything is computed
+      uint64_t raw[16];
+      bool run = false;
+      if (p.k_run >= 16 && h0 + 16 <= p.k) {
+        const int64_t r0 = p.k_run >= p.k ? h0 : h0 % p.k_run;
+        run = r0 + 16 <= p.k_run;  // the sixteen positions are adjacent in memory
+      }
+      if (run) {
+        const double* src = base + p.kv[h0];
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+          const ulonglong2* v = reinterpret_cast<const ulonglong2*>(src);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const ulonglong2 t = v[e];
+            raw[2 * e] = t.x;
+            raw[2 * e + 1] = t.y;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) raw[e] = static_cast<uint64_t>(__double_as_longlong(src[e]));
+        }
+      } else {
+        int64_t idx[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) idx[e] = h0 + e < p.k ? p.kv[h0 + e] : -1;
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          raw[e] = h0 + e < p.k ? static_cast<uint64_t>(__double_as_longlong(base[idx[e]])) : 0ull;
+      }
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
-        uint64_t u = 0;
-        if (h0 + e < p.k) u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h0 + e]]));
         if (WORDS == 2) {
-          dev::signed_digits64(dev::quantize_i64(u, sg, p.trunc != 0), &d0[e], &d1[e]);
+          dev::signed_digits64(dev::quantize_i64(raw[e], sg, p.trunc != 0), &d0[e], &d1[e]);
           d2[e] = 0;
         } else {
           uint64_t lo;
           uint32_t hi;
           bool neg;
-          dev::quantize(u, sg, p.trunc != 0, &lo, &hi, &neg);
+          dev::quantize(raw[e], sg, p.trunc != 0, &lo, &hi, &neg);
           dev::signed_digits96(lo, hi, neg, &d0[e], &d1[e], &d2[e]);
         }
       }
@@ -275,23 +325,22 @@ __device__ __noinline__ double native_dot(const double* a, const double* b, cons
 }
 
 // One output of the thread's four: flagged rows / columns take the native FMA chain.
-template <int NL, int LANE>
+template <int N, int LANE>
 __device__ __forceinline__ double crt_value(const CrtParams& p, const uint32_t* packed, int64_t lam,
                                             int64_t i, int64_t j, int si, bool fa, int tau, bool fb) {
-  constexpr int WORDS = dev::CrtShape<NL>::kWords;
+  constexpr int WORDS = dev::CrtShape<N>::kWords;
   if (fa || fb)
     return native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j],
                       p.v.a_k, p.v.b_k, p.k);
   uint32_t mag[WORDS];
-  bool neg;
-  dev::crt<NL, LANE>(p.t, packed, mag, &neg);
+  const bool neg = dev::crt<N, LANE>(p.t, packed, mag);
   return dev::round_scaled_fast<WORDS>(mag, neg, -(si + tau));
 }
 
 // One thread = 4 consecutive columns of one row of one batch. Grid: x (with 2^lg_fast threads of a
 // CTA) covers the column quads of a row, y and the remaining threads stride over the rows.
-template <int NL>
-__global__ void __launch_bounds__(kThreads) k_crt(const __grid_constant__ CrtParams p) {
+template <int N>
+__global__ void __launch_bounds__(kThreads, 3) k_crt(const __grid_constant__ CrtParams p) {
   const int64_t quads = p.n_hat >> 2;
   const int F = 1 << p.lg_fast, per = kThreads >> p.lg_fast;
   const int64_t jq = static_cast<int64_t>(blockIdx.x) * F + (threadIdx.x & (F - 1));
@@ -299,6 +348,13 @@ __global__ void __launch_bounds__(kThreads) k_crt(const __grid_constant__ CrtPar
   if (jq >= quads || j0 >= p.n) return;
   const int64_t plane = p.b * p.m * p.n_hat;
   const int64_t total_rows = p.b * p.m;
+  const int64_t left = p.n - j0;  // >= 1
+  // the thread's four outputs are adjacent in C and 16-byte aligned relative to the row start?
+  const int64_t c0 = p.v.c_col[j0];
+  const bool adjacent = left > 3 && p.v.c_col[j0 + 3] == c0 + 3 && p.v.c_col[j0 + 1] == c0 + 1 &&
+                        p.v.c_col[j0 + 2] == c0 + 2;
+  const int64_t c1 = left > 1 ? p.v.c_col[j0 + 1] : 0, c2 = left > 2 ? p.v.c_col[j0 + 2] : 0,
+                c3 = left > 3 ? p.v.c_col[j0 + 3] : 0;
   for (int64_t rho = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
        rho < total_rows; rho += static_cast<int64_t>(gridDim.y) * per) {
     int64_t lam = 0, i = rho;
@@ -307,45 +363,45 @@ __global__ void __launch_bounds__(kThreads) k_crt(const __grid_constant__ CrtPar
       i = rho - lam * p.m;
     }
     const uint8_t* w = p.W + rho * p.n_hat + j0;
-    uint32_t packed[kMaxModuli];
+    uint32_t packed[N];
 #pragma unroll
-    for (int l = 0; l < kMaxModuli; ++l)
-      packed[l] = l < p.t.N ? *reinterpret_cast<const uint32_t*>(w + l * plane) : 0u;
+    for (int l = 0; l < N; ++l) packed[l] = *reinterpret_cast<const uint32_t*>(w + l * plane);
     const int si = p.sigma[rho];
     const bool fa = p.fA[rho] != 0;
     const int16_t* tau = p.tau + lam * p.n + j0;
     const uint8_t* fb = p.fB + lam * p.n + j0;
-    const int64_t left = p.n - j0;  // >= 1
-    double D[4];
-    D[0] = crt_value<NL, 0>(p, packed, lam, i, j0, si, fa, tau[0], fb[0] != 0);
-    D[1] = left > 1 ? crt_value<NL, 1>(p, packed, lam, i, j0 + 1, si, fa, tau[1], fb[1] != 0) : 0.0;
-    D[2] = left > 2 ? crt_value<NL, 2>(p, packed, lam, i, j0 + 2, si, fa, tau[2], fb[2] != 0) : 0.0;
-    D[3] = left > 3 ? crt_value<NL, 3>(p, packed, lam, i, j0 + 3, si, fa, tau[3], fb[3] != 0) : 0.0;
+    double D0, D1 = 0.0, D2 = 0.0, D3 = 0.0;
+    D0 = crt_value<N, 0>(p, packed, lam, i, j0, si, fa, tau[0], fb[0] != 0);
+    if (left > 1) D1 = crt_value<N, 1>(p, packed, lam, i, j0 + 1, si, fa, tau[1], fb[1] != 0);
+    if (left > 2) D2 = crt_value<N, 2>(p, packed, lam, i, j0 + 2, si, fa, tau[2], fb[2] != 0);
+    if (left > 3) D3 = crt_value<N, 3>(p, packed, lam, i, j0 + 3, si, fa, tau[3], fb[3] != 0);
     double* crow = p.C + p.v.c_bat[lam] + p.v.c_row[i];
-    const int64_t c0 = p.v.c_col[j0];
     double* c = crow + c0;
-    // four adjacent, 32-byte aligned outputs go out as two 16-byte stores
-    if (left > 3 && p.v.c_col[j0 + 3] == c0 + 3 && p.v.c_col[j0 + 1] == c0 + 1 &&
-        p.v.c_col[j0 + 2] == c0 + 2 && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
-      double2* c2 = reinterpret_cast<double2*>(c);
-      double2 lo, hi;
+    if (adjacent && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+      double2* cv = reinterpret_cast<double2*>(c);
+      double2 lo = make_double2(0.0, 0.0), hi = lo;
       if (p.beta != 0.0) {
-        lo = c2[0];
-        hi = c2[1];
+        lo = cv[0];
+        hi = cv[1];
       }
-      lo.x = finish(D[0], p.alpha, p.beta, &lo.x);
-      lo.y = finish(D[1], p.alpha, p.beta, &lo.y);
-      hi.x = finish(D[2], p.alpha, p.beta, &hi.x);
-      hi.y = finish(D[3], p.alpha, p.beta, &hi.y);
-      c2[0] = lo;
-      c2[1] = hi;
+      lo.x = finish(D0, p.alpha, p.beta, &lo.x);
+      lo.y = finish(D1, p.alpha, p.beta, &lo.y);
+      hi.x = finish(D2, p.alpha, p.beta, &hi.x);
+      hi.y = finish(D3, p.alpha, p.beta, &hi.y);
+      cv[0] = lo;
+      cv[1] = hi;
     } else {
-      for (int e = 0; e < 4 && e < left; ++e) {
-        double* ce = crow + p.v.c_col[j0 + e];
-        *ce = finish(D[e], p.alpha, p.beta, ce);
-      }
+      *c = finish(D0, p.alpha, p.beta, c);
+      if (left > 1) crow[c1] = finish(D1, p.alpha, p.beta, crow + c1);
+      if (left > 2) crow[c2] = finish(D2, p.alpha, p.beta, crow + c2);
+      if (left > 3) crow[c3] = finish(D3, p.alpha, p.beta, crow + c3);
     }
   }
+}
+
+template <int N>
+void launch_crt(const CrtParams& p, dim3 grid, cudaStream_t stream) {
+  k_crt<N><<<grid, kThreads, 0, stream>>>(p);
 }
 
 // ---- degenerate paths --------------------------------------------------------------------------
@@ -590,6 +646,9 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
       p.k = e.k;
       p.k_hat = e.k_hat;
       p.rows_fast = e.rows_fast[x];
+      p.k_run = e.modes.count[kClsK] > 0 && e.modes.stride[e.modes.first[kClsK]][x] == 1
+                    ? e.modes.extent[e.modes.first[kClsK]]
+                    : 0;
       p.trunc = e.trunc;
       p.mod0 = g0;
       p.mods = mods;
@@ -633,17 +692,16 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   const int64_t gyq = (rows_total + perq - 1) / perq;
   const dim3 grid(static_cast<unsigned int>((quads + Fq - 1) / Fq),
                   static_cast<unsigned int>(gyq < 65535 ? gyq : 65535));
-  switch (plan.crt.nl) {
-    case 1: k_crt<1><<<grid, kThreads, 0, stream>>>(p); break;
-    case 2: k_crt<2><<<grid, kThreads, 0, stream>>>(p); break;
-    case 3: k_crt<3><<<grid, kThreads, 0, stream>>>(p); break;
-    case 4: k_crt<4><<<grid, kThreads, 0, stream>>>(p); break;
-    case 5: k_crt<5><<<grid, kThreads, 0, stream>>>(p); break;
-    case 6: k_crt<6><<<grid, kThreads, 0, stream>>>(p); break;
-    case 7: k_crt<7><<<grid, kThreads, 0, stream>>>(p); break;
-    case 8: k_crt<8><<<grid, kThreads, 0, stream>>>(p); break;
-    default: k_crt<9><<<grid, kThreads, 0, stream>>>(p); break;
+  switch (e.N) {
+#define IMD_CRT_CASE(n) case n: launch_crt<n>(p, grid, stream); break;
+    IMD_CRT_CASE(2) IMD_CRT_CASE(3) IMD_CRT_CASE(4) IMD_CRT_CASE(5) IMD_CRT_CASE(6)
+    IMD_CRT_CASE(7) IMD_CRT_CASE(8) IMD_CRT_CASE(9) IMD_CRT_CASE(10) IMD_CRT_CASE(11)
+    IMD_CRT_CASE(12) IMD_CRT_CASE(13) IMD_CRT_CASE(14) IMD_CRT_CASE(15) IMD_CRT_CASE(16)
+    IMD_CRT_CASE(17) IMD_CRT_CASE(18) IMD_CRT_CASE(19) IMD_CRT_CASE(20)
+#undef IMD_CRT_CASE
+    default: return IMD_STATUS_INVALID_VALUE;
   }
+  if (plan.crt.nl != dev::crt_limbs_of(e.N)) return IMD_STATUS_CUDA_ERROR;  // tables out of step
   mark(4, stream);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
