@@ -205,6 +205,10 @@ IMD_API int imd_test_use_reference_gemm(int on) {
   imd::use_reference_gemm() = on != 0;
   return 0;
 }
+IMD_API int imd_test_gemm_variant(int v) {
+  imd::gemm_variant() = v;
+  return 0;
+}
 /* Reads (and clears) the sticky device error word: nonzero when a bounded wait in a kernel gave
  * up. Synchronises the device. */
 IMD_API unsigned int imd_test_device_error(void) {

@@ -364,6 +364,249 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   }
 }
 
+// ---- CTA-pair variant ---------------------------------------------------------------------------
+// Two CTAs of a cluster (two SMs) share one 256 x 256 tile: each loads its own 128 rows of A and its
+// own 128 of the 256 rows of B, and one tcgen05.mma.cta_group::2 of the leader CTA (rank 0) drives
+// both tensor cores, each accumulating its 128 rows in its own tensor memory. Per SM this halves
+// the B bytes that are written to and read from shared memory, which is what bounds the 1-CTA
+// kernel (TMA writes plus operand reads exceed the shared-memory port). Signals:
+//   full[s]    in the leader: its producer arms it with the bytes of both CTAs; every TMA load of
+//              either CTA completes on it (cp.async.bulk.tensor with .cta_group::2, no multicast)
+//   empty[s]   in each CTA: tcgen05.commit of the leader arrives on both (commit multicast)
+//   tfull[a]   in each CTA: same commit multicast after the last K block of a tile
+//   tempty[a]  in the leader: the eight epilogue warps of both CTAs arrive (the peer's remotely)
+constexpr int kPairStages = 6;
+constexpr int kPairBytesB = 128 * kTileK;
+constexpr int kPairStageBytes = kBytesA + kPairBytesB;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr uint32_t kPairInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) |
+                                    (static_cast<uint32_t>(256 >> 3) << 17) |
+                                    (static_cast<uint32_t>(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
+                   : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map,
+                                                 uint32_t leader_bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in the CTAs of `mask` (bit r = CTA rank r)
+// once every tcgen05.mma issued so far by this thread has retired.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask = 3) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(bar), "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Work item -> (plane, 256-row tile, 256-column tile), bands of 8 tile rows.
+__device__ __forceinline__ TileCoord pair_tile_of(const GemmParams& p, int64_t w) {
+  const int per_plane = p.tiles_m * p.tiles_n;
+  TileCoord c;
+  c.plane = static_cast<int>(w / per_plane);
+  const int t = static_cast<int>(w % per_plane);
+  const int band = 8 * p.tiles_n;
+  const int first = (t / band) * 8;
+  const int rows = min(p.tiles_m - first, 8);
+  const int r = t % band;
+  c.tm = first + r % rows;
+  c.tn = r / rows;
+  return c;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  uint8_t* ctrl = smem_raw + (tiles - raw) + kPairStages * kPairStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[6] empty[6] tfull[2] tempty[2] drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 160);
+  volatile int* abort = reinterpret_cast<volatile int*>(ctrl + 168);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (kPairStages + s); };
+  auto tfull = [&](int a) { return bar0 + 8u * (2 * kPairStages + a); };
+  auto tempty = [&](int a) { return bar0 + 8u * (2 * kPairStages + 2 + a); };
+  const uint32_t drain = bar0 + 8u * (2 * kPairStages + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull(a), 1);
+      mbar_init(tempty(a), 8);
+    }
+    mbar_init(drain, 1);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int64_t total = static_cast<int64_t>(p.s.planes) * p.tiles_m * p.tiles_n;
+  const int64_t first = blockIdx.x >> 1, step = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool okay = true;
+      for (int64_t w = first; w < total && okay; w += step) {
+        const TileCoord c = pair_tile_of(p, w);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty(stage), phase ^ 1u, abort)) {
+            okay = false;
+            break;
+          }
+          const uint32_t leader_full = map_to_cta(full(stage), 0);
+          if (leader) mbar_expect_tx(full(stage), 2 * kPairStageBytes);
+          const uint32_t dst = tiles + stage * kPairStageBytes;
+          const int kx = p.s.k0 + kb * kTileK;
+          tma_load_3d_pair(dst, &map_a, leader_full, kx, c.tm * 256 + static_cast<int>(rank) * 128,
+                           c.plane);
+          tma_load_3d_pair(dst + kBytesA, &map_b, leader_full, kx,
+                           c.tn * 256 + static_cast<int>(rank) * 128, c.plane);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && leader) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool okay = true;
+      for (int64_t w = first; w < total && okay; w += step) {
+        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccCols;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full(stage), phase, abort)) {
+            okay = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = tiles + stage * kPairStageBytes, b_addr = a_addr + kBytesA;
+#pragma unroll
+          for (int k4 = 0; k4 < kTileK / kMmaK; ++k4)
+            tc_mma_i8_pair(d_tmem, smem_desc(a_addr + k4 * kMmaK), smem_desc(b_addr + k4 * kMmaK),
+                           kPairInstrDesc, (kb | k4) != 0 ? 1u : 0u);
+          tc_commit_pair(empty(stage));
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!okay) break;
+        tc_commit_pair(tfull(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      tc_commit_pair(drain, 1);  // every MMA issued above has retired once this arrives
+      for (uint32_t it = 0; it < kSpinLimit; ++it)
+        if (mbar_try_wait(drain, 0)) break;
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int64_t w = first; w < total; w += step) {
+      const TileCoord c = pair_tile_of(p, w);
+      if (!mbar_wait(tfull(acc), acc_phase, abort)) break;
+      tc_fence_after();
+      const int slot = c.plane / p.s.batches, lam = c.plane % p.s.batches;
+      const uint32_t pm = p.s.p[slot], magic = p.s.magic[slot], bias = p.s.bias[slot];
+      const uint32_t magic_up = p.s.magic_up[slot], qm = p.s.q[slot];
+      const int row = c.tm * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const int64_t wplane = static_cast<int64_t>(p.s.mod0 + slot) * p.s.batches + lam;
+      uint8_t* wrow = p.W + (wplane * p.s.m + row) * static_cast<int64_t>(p.s.n_hat);
+      const uint32_t taddr = tmem_base + acc * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int cc = 0; cc < 256 / 32; ++cc) {
+        const int col = c.tn * 256 + cc * 32;
+        if (col >= p.s.n_hat) break;
+        uint32_t v[32];
+        tmem_load_32(taddr + cc * 32, v);
+        if (row < p.s.m) {
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            if (col + 16 * hf < p.s.n_hat) {
+              uint4* dst = reinterpret_cast<uint4*>(wrow + col + 16 * hf);
+              uint4 prev = make_uint4(0, 0, 0, 0);
+              if (p.s.add) prev = *dst;
+              *dst = reduce16(v + 16 * hf, prev, p.s.add != 0, pm, magic, magic_up, bias, qm);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty(acc), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();  // no CTA leaves while its peer may still signal it or write its tensor memory
+  if (threadIdx.x == 0 && *abort) atomicOr(p.error_word, 2u);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -394,7 +637,9 @@ imd_status_t gemm_setup(GemmPlanInfo* info) {
     return IMD_STATUS_CUDA_ERROR;
   }
   if (cudaFuncSetAttribute(k_gemm_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-      cudaSuccess) {
+          cudaSuccess ||
+      cudaFuncSetAttribute(k_gemm_i8_pair, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kPairSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return IMD_STATUS_CUDA_ERROR;
   }
@@ -411,22 +656,35 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
                          const int8_t* RB, uint8_t* W, cudaStream_t stream) {
   if (info.encode_tiled == nullptr || info.error_word == nullptr) return IMD_STATUS_CUDA_ERROR;
   const EncodeTiled fn = reinterpret_cast<EncodeTiled>(info.encode_tiled);
+  const int variant = gemm_variant();
+  const bool pair = variant == 2 || (variant == 0 && s.m > kTileM);
   CUtensorMap map_a, map_b;
   if (!encode_planes(fn, &map_a, RA, s.k_hat, s.m, s.planes, kTileM) ||
-      !encode_planes(fn, &map_b, RB, s.k_hat, s.n_hat, s.planes, kTileN))
+      !encode_planes(fn, &map_b, RB, s.k_hat, s.n_hat, s.planes, pair ? 128 : kTileN))
     return IMD_STATUS_CUDA_ERROR;
   GemmParams p{};
   p.s = s;
-  p.tiles_m = (s.m + kTileM - 1) / kTileM;
+  p.tiles_m = (s.m + (pair ? 256 : kTileM) - 1) / (pair ? 256 : kTileM);
   p.tiles_n = (s.n_hat + kTileN - 1) / kTileN;
   p.k_blocks = (s.klen + kTileK - 1) / kTileK;
   p.W = W;
   p.error_word = info.error_word;
   const int64_t total = static_cast<int64_t>(s.planes) * p.tiles_m * p.tiles_n;
   const int sms = info.sms > 0 ? info.sms : kDefaultSms;
-  const unsigned int grid = static_cast<unsigned int>(total < sms ? total : sms);
-  k_gemm_i8<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  if (pair) {
+    const int64_t pairs = total < sms / 2 ? total : sms / 2;
+    k_gemm_i8_pair<<<static_cast<unsigned int>(2 * pairs), kGemmThreads, kPairSmemBytes, stream>>>(
+        map_a, map_b, p);
+  } else {
+    const unsigned int grid = static_cast<unsigned int>(total < sms ? total : sms);
+    k_gemm_i8<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  }
   return cudaPeekAtLastError() == cudaSuccess ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+int& gemm_variant() {
+  static int v = 0;  // verification hook: 0 = by shape, 1 = one CTA per tile, 2 = CTA pairs
+  return v;
 }
 
 }  // namespace imd

@@ -52,6 +52,9 @@ imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stre
 
 // Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.
 bool& use_reference_gemm();
+// Verification switch for the tensor-core kernel: 0 = chosen by shape, 1 = one CTA per 128 x 256
+// tile, 2 = CTA pairs on 256 x 256 tiles.
+int& gemm_variant();
 
 // Benchmark-only phase timing (tags: 1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate path).
 int profile_enable(int capacity);

@@ -50,11 +50,12 @@ class Workspace:
 
 
 def run_descs(descs, bufs, bases, alpha, beta, N, g=0, rounding="RN", mode="EMULATE",
-              vec_mode="GENERATE", reference_gemm=False, want_ws=False):
+              vec_mode="GENERATE", reference_gemm=False, want_ws=False, gemm_variant=0):
     """imd_plan_create + imd_contract on flat float64 buffers with raw descriptors. Returns the
     whole C buffer (numpy) and, optionally, (plan, workspace)."""
     L = lib()
     L.lib.imd_test_use_reference_gemm(1 if reference_gemm else 0)
+    L.lib.imd_test_gemm_variant(gemm_variant)
     try:
         plan = imd.Plan.from_descs(*descs, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode)
         dA, dB, dC = (dev_f64(b) if b is not None else None for b in bufs)
@@ -69,6 +70,7 @@ def run_descs(descs, bufs, bases, alpha, beta, N, g=0, rounding="RN", mode="EMUL
         out = host_f64(dC)
     finally:
         L.lib.imd_test_use_reference_gemm(0)
+        L.lib.imd_test_gemm_variant(0)
     if want_ws:
         return out, plan, ws
     plan.close()

@@ -114,6 +114,9 @@ def test_random_against_oracle(m, n, k, N, kind, alpha, beta):
         outs.append(out)
     ref = gu.run_descs(descs, (A, Bt, Cin), (0, 0, 0), alpha, beta, N, reference_gemm=True)
     assert same_bits(ref, outs[0])
+    for variant in (1, 2):   # one CTA per tile / CTA pairs, whatever the shape rule would pick
+        out = gu.run_descs(descs, (A, Bt, Cin), (0, 0, 0), alpha, beta, N, gemm_variant=variant)
+        assert same_bits(out, outs[0])
 
 
 def test_k_chunks_carry_mod_p():
@@ -123,9 +126,9 @@ def test_k_chunks_carry_mod_p():
     A, Bt, _ = _random_case(3, m, n, k, "uniform")
     descs = gu.matrix_descs(m, n, k)
     want = orc.gemm(A, Bt, N, 1.0, 0.0, None, "TRUNC")
-    for refg in (True, False):
+    for refg, variant in ((True, 0), (False, 1), (False, 2)):
         out = gu.run_descs(descs, (A, Bt, np.zeros((m, n))), (0, 0, 0), 1.0, 0.0, N,
-                           rounding="TRUNC", reference_gemm=refg)
+                           rounding="TRUNC", reference_gemm=refg, gemm_variant=variant)
         assert same_bits(out.reshape(m, n), want)
 
 
