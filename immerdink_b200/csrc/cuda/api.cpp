@@ -205,6 +205,14 @@ IMD_API int imd_test_use_reference_gemm(int on) {
   imd::use_reference_gemm() = on != 0;
   return 0;
 }
+/* Benchmark-only: measured ceiling of the int8 tensor pipe (ops/s) for the GEMM's tile shapes. */
+IMD_API double imd_prof_mma_peak(int pair) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return 0.0;
+  return imd::mma_probe_tops(pair, sms);
+}
 IMD_API int imd_test_gemm_variant(int v) {
   imd::gemm_variant() = v;
   return 0;

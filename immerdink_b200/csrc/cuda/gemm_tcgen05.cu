@@ -607,6 +607,57 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---- tensor-pipe probe ---------------------------------------------------------------------------
+// Issues tcgen05.mma.kind::i8 back to back on whatever the shared memory holds (no loads, results
+// discarded): the time gives the ceiling of the int8 tensor pipe for the tile shapes used above,
+// the denominator of the GEMM roofline. pair = 0: M128 N256 per CTA; pair = 1: M256 N256 per CTA pair.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64, 1) k_mma_probe(int iters, int pair) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t rank = cluster_rank();
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (threadIdx.x == 0 && (!pair || rank == 0)) {
+    uint32_t phase = 0;
+    for (int it = 0; it < iters; it += 64) {
+      for (int j = 0; j < 64; ++j) {
+        const uint32_t a = tiles + (j & 3) * kMmaK, b = tiles + kBytesA + (j & 3) * kMmaK;
+        if (pair) tc_mma_i8_pair(tmem_base + (j & 1) * kAccCols, smem_desc(a), smem_desc(b), kPairInstrDesc, 1u);
+        else tc_mma_i8(tmem_base + (j & 1) * kAccCols, smem_desc(a), smem_desc(b), kInstrDesc, 1u);
+      }
+      if (pair) tc_commit_pair(smem_u32(&bar), 1);
+      else tc_commit(smem_u32(&bar));
+      for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait(smem_u32(&bar), phase)) break;
+      phase ^= 1u;
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -680,6 +731,29 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
     k_gemm_i8<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_a, map_b, p);
   }
   return cudaPeekAtLastError() == cudaSuccess ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+// int8 ops per second of the bare tensor pipe (see k_mma_probe); 0 on failure. Synchronises.
+double mma_probe_tops(int pair, int sms) {
+  const int smem = kBytesA + kBytesB + 2048;
+  if (cudaFuncSetAttribute(k_mma_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return 0.0;
+  const int iters = 64 * 256;
+  const int grid = sms / 2 * 2;
+  cudaEvent_t e0, e1;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return 0.0;
+  k_mma_probe<<<grid, 64, smem>>>(64, pair);  // warm-up
+  cudaEventRecord(e0);
+  k_mma_probe<<<grid, 64, smem>>>(iters, pair);
+  cudaEventRecord(e1);
+  float ms = 0;
+  const bool ok = cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (!ok || ms <= 0) return 0.0;
+  const double issuers = pair ? grid / 2 : grid;
+  const double ops = 2.0 * (pair ? 256.0 : 128.0) * 256.0 * 32.0 * iters * issuers;
+  return ops / (ms * 1e-3);
 }
 
 int& gemm_variant() {

@@ -55,6 +55,8 @@ bool& use_reference_gemm();
 // Verification switch for the tensor-core kernel: 0 = chosen by shape, 1 = one CTA per 128 x 256
 // tile, 2 = CTA pairs on 256 x 256 tiles.
 int& gemm_variant();
+// Benchmark hook: int8 ops per second of back-to-back tcgen05.mma.kind::i8 with no loads.
+double mma_probe_tops(int pair, int sms);
 
 // Benchmark-only phase timing (tags: 1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate path).
 int profile_enable(int capacity);

@@ -692,6 +692,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   const int64_t gyq = (rows_total + perq - 1) / perq;
   const dim3 grid(static_cast<unsigned int>((quads + Fq - 1) / Fq),
                   static_cast<unsigned int>(gyq < 65535 ? gyq : 65535));
+  if (plan.crt.nl != dev::crt_limbs_of(e.N)) return IMD_STATUS_CUDA_ERROR;  // tables out of step
   switch (e.N) {
 #define IMD_CRT_CASE(n) case n: launch_crt<n>(p, grid, stream); break;
     IMD_CRT_CASE(2) IMD_CRT_CASE(3) IMD_CRT_CASE(4) IMD_CRT_CASE(5) IMD_CRT_CASE(6)
@@ -701,7 +702,6 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
 #undef IMD_CRT_CASE
     default: return IMD_STATUS_INVALID_VALUE;
   }
-  if (plan.crt.nl != dev::crt_limbs_of(e.N)) return IMD_STATUS_CUDA_ERROR;  // tables out of step
   mark(4, stream);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
