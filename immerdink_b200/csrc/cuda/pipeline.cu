@@ -14,6 +14,7 @@
 // (src/contract.cu:1334-1485) and its kernels K0, K1, K2/K3, KF, KL, K5, k_direct,
 // k5_beta_only; the numerics are in numerics.cuh.
 #include <cstdint>
+#include <mutex>
 #include <vector>
 
 #include "kernels.hpp"
@@ -706,4 +707,59 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
 
+// ---- built-in workspace ---------------------------------------------------------------------------
+// A fixed workspace that lives in the library image, for callers that are not in a position to
+// allocate device memory. The name below is only a handle on the host side: its device address is
+// looked up once per device (with that device current) and that pointer is what the kernels get.
+namespace {
+
+constexpr size_t kBuiltinWorkspaceBytes = IMD_BUILTIN_WS_BYTES;  // per GPU that loads the library
+constexpr int kBuiltinMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_builtin_workspace[kBuiltinWorkspaceBytes];
+
+std::mutex g_builtin_lock;
+void* g_builtin_ptr[kBuiltinMaxDevices] = {};
+
+}  // namespace
+
+// Device address of the built-in workspace on the current device; looked up on the first call per
+// device, cached afterwards. No allocation.
+imd_status_t builtin_workspace(void** ptr, size_t* bytes) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kBuiltinMaxDevices) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
+  std::lock_guard<std::mutex> hold(g_builtin_lock);
+  if (g_builtin_ptr[device] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_builtin_workspace) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return IMD_STATUS_CUDA_ERROR;
+    }
+    g_builtin_ptr[device] = p;
+  }
+  *ptr = g_builtin_ptr[device];
+  *bytes = kBuiltinWorkspaceBytes;
+  return IMD_STATUS_SUCCESS;
+}
+
 }  // namespace imd
+
+extern "C" {
+
+// imd_contract on the library's built-in workspace (see immerdink.h). Allocates nothing.
+IMD_API imd_status_t imd_contract_builtin_ws(imd_plan_t plan, double alpha, const double* A,
+                                             const double* B, double beta, double* C,
+                                             cudaStream_t stream) {
+  if (plan == nullptr) return IMD_STATUS_INVALID_VALUE;
+  if (plan->exec.layout.total > imd::kBuiltinWorkspaceBytes)
+    return IMD_STATUS_INSUFFICIENT_WORKSPACE;  // this contraction needs more than the fixed 32 MiB
+  void* ws = nullptr;
+  size_t bytes = 0;
+  if (const imd_status_t st = imd::builtin_workspace(&ws, &bytes); st != IMD_STATUS_SUCCESS)
+    return st;
+  return imd_contract(plan, alpha, A, B, beta, C, ws, bytes, stream);
+}
+
+}  // extern "C"

@@ -77,6 +77,28 @@ IMD_API imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const im
                                          const imd_operand_t* B, double beta, double* C,
                                          void* ws, size_t ws_bytes, cudaStream_t stream);
 
+/* imd_contract without a caller-supplied workspace (no counterpart in the reference).
+ *
+ * For callers that cannot obtain device memory at the point of the call: a plugin running inside
+ * a host application whose device memory pool is closed to cudaMalloc, or code on a
+ * latency-critical path where a driver allocation (which may synchronise the whole device) is not
+ * acceptable. The workspace is a fixed IMD_BUILTIN_WS_BYTES array inside the library image, so
+ * every GPU that loads libimmerdink.so gives up that much memory until the process exits.
+ *
+ * Same checks, statuses and results as imd_contract, except that a plan whose imd_workspace_size
+ * exceeds IMD_BUILTIN_WS_BYTES is refused with IMD_STATUS_INSUFFICIENT_WORKSPACE (nothing is
+ * touched). The call allocates nothing, neither directly nor through a library.
+ *   - The first call on each device looks up the array's device address (the plan's device must be
+ *     current, as for imd_contract); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array: two calls whose GPU work can overlap (different
+ *     streams, or threads) race on it. Order them on one stream or with events.
+ *   - The array keeps whatever the previous call left there. Nothing in it needs to start at zero:
+ *     every byte a kernel reads is written earlier in the same call. */
+#define IMD_BUILTIN_WS_BYTES (32u << 20)
+IMD_API imd_status_t imd_contract_builtin_ws(imd_plan_t plan, double alpha, const double* A,
+                                             const double* B, double beta, double* C,
+                                             cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
