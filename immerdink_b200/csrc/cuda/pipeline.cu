@@ -151,8 +151,10 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
   const bool any = (gf & 0xFFFF) != 0;
   const int gamma = (gf & 0xFFFF) - 2048;
 
-  // pass 2: S = sum ceil(x^2 2^60), exact in 128 bits, order-independent
-  uint64_t hi = 0, lo = 0;
+  // pass 2, fast: an FP64 sum of squares of x = a 2^-gamma encloses the exact S (each ceil adds
+  // less than 1; k fused multiply-adds of positive terms err by at most (k + 512) 2^-52 relative,
+  // taken twice over). If both ends of the enclosure give the same shift, that is the shift.
+  double acc = 0.0;
   if (live && any)
     for (int64_t h = kl; h < p.k; h += 4 * KT) {
       uint64_t u[4];
@@ -163,31 +165,84 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
+        const int ef = static_cast<int>(u[j] >> 52) & 0x7FF;
+        const int xe = ef - gamma;  // exponent field of x; <= 0: x^2 is far below the enclosure width
+        if (ef != 0 && ef != 0x7FF && xe > 0) {
+          const double x = __longlong_as_double(static_cast<long long>(
+              (u[j] & 0x000FFFFFFFFFFFFFull) | (static_cast<uint64_t>(xe) << 52)));
+          acc = __fma_rn(x, x, acc);
+        }
+      }
+    }
+  double* s_acc = reinterpret_cast<double*>(s_hi);
+  s_acc[slot] = acc;
+  __syncthreads();
+  for (int s = KT >> 1; s > 0; s >>= 1) {
+    if (kl < s) s_acc[slot] += s_acc[slot + s];
+    __syncthreads();
+  }
+  int sg = 0;
+  int exact = 0;
+  if (live && kl == 0 && any) {
+    const double sum = s_acc[slot];
+    const double eps = (static_cast<double>(p.k) + 512.0) * 0x1p-51;
+    // the enclosure needs a normal gamma, a sane k and a sum that saw the largest entry
+    if (gamma < -900 || p.k > (int64_t{1} << 36) || !(sum >= 0.99)) {
+      exact = 1;
+    } else {
+      const double lo_d = sum - sum * eps, hi_d = sum + sum * eps;
+      // d 2^60 as a 128-bit integer: floor for the lower end, ceil + k + 1 for the upper end
+      auto to_u128 = [](double d, bool up, uint64_t* h, uint64_t* l) {
+        const uint64_t bits = static_cast<uint64_t>(__double_as_longlong(d));
+        const uint64_t m = (bits & 0x000FFFFFFFFFFFFFull) | (1ull << 52);
+        const int sh = static_cast<int>(bits >> 52) - 1023 - 52 + kFracBits;  // >= 7 as d >= 0.98
+        *l = sh >= 64 ? 0 : m << sh;
+        *h = sh >= 64 ? m << (sh - 64) : (sh == 0 ? 0 : m >> (64 - sh));
+        (void)up;
+      };
+      uint64_t lh, ll, hh, hl;
+      to_u128(lo_d, false, &lh, &ll);
+      to_u128(hi_d, true, &hh, &hl);
+      const uint64_t add = static_cast<uint64_t>(p.k) + 1;
+      hl += add;
+      hh += hl < add ? 1 : 0;
+      const int s_small = dev::shift_from_sum(hh, hl, p.lhs_shift, p.rhs, gamma);  // largest S
+      const int s_large = dev::shift_from_sum(lh, ll, p.lhs_shift, p.rhs, gamma);  // smallest S
+      sg = s_small;
+      exact = s_small != s_large;
+    }
+  }
+  // exact integer pass, for every row of the CTA, when any of its rows could not be decided
+  if (__syncthreads_or(exact)) {
+    uint64_t hi = 0, lo = 0;
+    if (live && any)
+      for (int64_t h = kl; h < p.k; h += KT) {
+        const uint64_t u = static_cast<uint64_t>(__double_as_longlong(base[p.kv[h]]));
         uint64_t M;
         int E;
-        if (dev::decompose(u[j], &M, &E) == 1) {
+        if (dev::decompose(u, &M, &E) == 1) {
           uint64_t th, tl;
           dev::square_term(M, E, gamma, &th, &tl);
           lo += tl;
           hi += th + (lo < tl ? 1 : 0);
         }
       }
-    }
-  s_hi[slot] = hi;
-  s_lo[slot] = lo;
-  __syncthreads();
-  for (int s = KT >> 1; s > 0; s >>= 1) {
-    if (kl < s) {
-      const uint64_t bl = s_lo[slot + s];
-      const uint64_t nl = s_lo[slot] + bl;
-      s_hi[slot] += s_hi[slot + s] + (nl < bl ? 1 : 0);
-      s_lo[slot] = nl;
-    }
+    s_hi[slot] = hi;
+    s_lo[slot] = lo;
     __syncthreads();
+    for (int s = KT >> 1; s > 0; s >>= 1) {
+      if (kl < s) {
+        const uint64_t bl = s_lo[slot + s];
+        const uint64_t nl = s_lo[slot] + bl;
+        s_hi[slot] += s_hi[slot + s] + (nl < bl ? 1 : 0);
+        s_lo[slot] = nl;
+      }
+      __syncthreads();
+    }
+    if (live && kl == 0 && any)
+      sg = dev::shift_from_sum(s_hi[slot], s_lo[slot], p.lhs_shift, p.rhs, gamma);
   }
   if (live && kl == 0) {
-    int sg = 0;
-    if (any) sg = dev::shift_from_sum(s_hi[slot], s_lo[slot], p.lhs_shift, p.rhs, gamma);
     p.sigma[rho] = static_cast<int16_t>(sg);
     p.flag[rho] = (gf >> 30) & 1;
   }
