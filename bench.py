@@ -14,9 +14,11 @@ moduli, residue group 7, alpha = 1, beta = 0, seeded synthetic uniform [-1, 1) o
   --impl reference  times that CPU oracle alone, all host threads (the reference has no other CPU
          implementation that can travel to the GPU box: its own is Python, spec/oracle.py)
 
-With N > 1 ranks (torchrun) the output C is partitioned over its free modes a and b; every rank
-holds the operand slabs of its tile and computes it with its own plan (no data-path collective:
-the slabs a rank needs are resident), strong scaling of the one contraction.
+With N > 1 ranks (torchrun) the output C is partitioned over its free modes a and b
+(immerdink_b200.dist): every rank owns 1/N of A and of B, all-gathers the slabs of its tile over
+NCCL inside its grid column / row, and computes the tile with its own plan; no collective follows.
+`value` times the contraction with the slabs gathered (strong scaling of the one contraction);
+the all-gather is timed separately (`exchange_ms`, `value_with_exchange`).
 """
 import argparse
 import json
@@ -230,13 +232,36 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    prob = Problem(args.workload, rank, world)
+    from immerdink_b200 import dist as idist
+    prob = Problem(args.workload, 0, 1)          # the undivided contraction
     lib = imd.load_library()
+    part = idist.Partition(prob.spec, prob.ext, world, rank, "a", "b")
 
-    A = prob.device_operand(0, dev)
-    B = prob.device_operand(1, dev)
-    Cd = torch.empty(prob.shape(2), dtype=torch.float64, device=dev)
-    plan = imd.Plan(prob.spec, A, B, Cd, N=prob.N, g=prob.g)
+    def synth(x, shape, start):
+        labels = prob.labels[x]
+        off = slab_offsets_torch(shape, prob.shape(x, False), [start.get(c, 0) for c in labels], dev)
+        return mix_torch(off, prob.seeds[x]).contiguous()
+
+    exchange = None
+    if world == 1:
+        A = synth(0, prob.shape(0), {})
+        B = synth(1, prob.shape(1), {})
+        Cd = torch.empty(prob.shape(2), dtype=torch.float64, device=dev)
+        plan = imd.Plan(prob.spec, A, B, Cd, N=prob.N, g=prob.g)
+        run_spec = prob.spec
+    else:
+        shard_a = synth(0, part.shard_shape(0), part.shard_start(0))
+        shard_b = synth(1, part.shard_shape(1), part.shard_start(1))
+        A = torch.empty(part.gathered_shape(0), dtype=torch.float64, device=dev)
+        B = torch.empty(part.gathered_shape(1), dtype=torch.float64, device=dev)
+        groups = idist.make_groups(world, dist)
+
+        def exchange():
+            idist.gather(part, shard_a, shard_b, A, B, groups, dist)
+        exchange()
+        run_spec, _, _, lc = part.plan_layouts()
+        Cd = torch.empty(lc.shape, dtype=torch.float64, device=dev)
+        plan = imd.Plan(run_spec, A, B, Cd, N=prob.N, g=prob.g)
     ws = torch.empty(plan.workspace_bytes + 256, dtype=torch.uint8, device=dev)
     off = (-ws.data_ptr()) % 256
     wsv = ws[off:off + plan.workspace_bytes]
@@ -282,17 +307,21 @@ def run_ours(args, rank, world, local_rank):
     ms_max = float(t_ms.item())
 
     # ---- end to end: pinned host operands in, host result out, through the public Python API
-    hA = torch.empty(A.shape, dtype=torch.float64).pin_memory()
-    hB = torch.empty(B.shape, dtype=torch.float64).pin_memory()
+    srcA, srcB = (A, B) if world == 1 else (shard_a, shard_b)
+    hA = torch.empty(srcA.shape, dtype=torch.float64).pin_memory()
+    hB = torch.empty(srcB.shape, dtype=torch.float64).pin_memory()
     hC = torch.empty(Cd.shape, dtype=torch.float64).pin_memory()
-    hA.copy_(A)
-    hB.copy_(B)
-    dA2, dB2 = torch.empty_like(A), torch.empty_like(B)
+    hA.copy_(srcA)
+    hB.copy_(srcB)
+    dA2, dB2 = (torch.empty_like(A), torch.empty_like(B)) if world == 1 else (shard_a, shard_b)
+    inA, inB = (dA2, dB2) if world == 1 else (A, B)
 
     def e2e_step():
         dA2.copy_(hA, non_blocking=True)
         dB2.copy_(hB, non_blocking=True)
-        imd.contract(prob.spec, dA2, dB2, Cd, N=prob.N, g=prob.g, workspace=wsv, stream=stream)
+        if exchange is not None:
+            exchange()
+        imd.contract(run_spec, inA, inB, Cd, N=prob.N, g=prob.g, workspace=wsv, stream=stream)
         hC.copy_(Cd, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 5))
@@ -308,6 +337,19 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_ms = float(t_e2e.item())
+    exchange_ms = 0.0
+    if exchange is not None:
+        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        exchange()
+        barrier()
+        x0.record(stream)
+        for _ in range(5):
+            exchange()
+        x1.record(stream)
+        barrier()
+        t_x = torch.tensor([x0.elapsed_time(x1) / 5], dtype=torch.float64, device=dev)
+        dist.all_reduce(t_x, op=dist.ReduceOp.MAX)
+        exchange_ms = float(t_x.item())
     err = lib.lib.imd_test_device_error()
 
     if rank != 0:
@@ -335,13 +377,16 @@ def run_ours(args, rank, world, local_rank):
                 dtype="int8xint8->int32 (FP64 emulation)", data="synthetic",
                 config=dict(workload=f"{args.workload}: {prob.spec} {prob.ext} N={prob.N} g={prob.g} "
                                      "alpha=1 beta=0, uniform[-1,1)",
-                            partition=f"C modes (a,b) over {GRID[world]} ranks, slabs resident",
+                            partition=f"C modes (a,b) over {GRID[world]} ranks; slabs all-gathered over "
+                                      "NCCL before the timed contraction",
+                            exchange_ms=exchange_ms,
+                            value_with_exchange=flops / ((ms_max + exchange_ms) * 1e-3) / 1e12,
                             l2="256 MB buffer written between timed steps",
                             gemm_view=[low["m"], low["n"], low["k"], low["b"]]),
                 e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOPS-eq",
-                         h2d_bytes_per_step=(A.numel() + B.numel()) * 8 * world,
+                         h2d_bytes_per_step=(srcA.numel() + srcB.numel()) * 8 * world,
                          d2h_bytes_per_step=Cd.numel() * 8 * world, ms_per_step=e2e_ms),
-                gpu_launches=int(low["kernel_launches"]) * args.steps,
+                gpu_launches=int(low["kernel_launches"]) * args.steps * world,
                 clocks=clocks,
                 phases_ms=phase_ms,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peak_tops, unit="TOP/s (int8)",

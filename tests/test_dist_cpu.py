@@ -1,0 +1,93 @@
+"""Multi-rank partition of one contraction (immerdink_b200.dist) on CPU ranks over gloo: every rank
+gathers its operand slabs, contracts its tile on the gathered buffers through the split-label
+descriptors, and the tiles together equal the undivided result bit for bit. The CPU oracle stands
+in for the device library here (host-side logic only)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SPEC = "kjbc,kiac->abij"
+EXT = dict(a=8, b=8, c=5, i=2, j=3, k=2)
+
+
+def _dense(labels, ext):
+    st, acc = [], 1
+    for c in reversed(labels):
+        st.append(acc)
+        acc *= ext[c]
+    return [ext[c] for c in labels], list(reversed(st))
+
+
+def _full_problem():
+    rng = np.random.default_rng(11)
+    A = rng.uniform(-1, 1, [EXT[c] for c in "kjbc"])
+    B = rng.uniform(-1, 1, [EXT[c] for c in "kiac"])
+    return A, B
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import imd_oracle as orc
+    from immerdink_b200 import dist as idist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    part = idist.Partition(SPEC, EXT, world, rank, "a", "b")
+    A, B = _full_problem()
+    # this rank's pieces
+    sa = part.shard_start(0)["b"]
+    sb = part.shard_start(1)["a"]
+    shard_a = torch.from_numpy(np.ascontiguousarray(A[:, :, sa:sa + part.piece_b, :]))
+    shard_b = torch.from_numpy(np.ascontiguousarray(B[:, :, sb:sb + part.piece_a, :]))
+    out_a = torch.empty(part.gathered_shape(0), dtype=torch.float64)
+    out_b = torch.empty(part.gathered_shape(1), dtype=torch.float64)
+    groups = idist.make_groups(world, dist)
+    idist.gather(part, shard_a, shard_b, out_a, out_b, groups, dist)
+    spec, la, lb, lc = part.plan_layouts()
+    ins, outl = spec.split("->")
+    labs = ins.split(",") + [outl]
+    descs = [orc.Desc(l.shape, l.strides, [ord(c) for c in lab]) for l, lab in zip((la, lb, lc), labs)]
+    tile = orc.contract_tensor(out_a.numpy().reshape(-1), out_b.numpy().reshape(-1),
+                               np.zeros(int(np.prod(lc.shape))), descs[0], descs[1], descs[2],
+                               1.0, 0.0, 14)
+    np.save(os.path.join(out_dir, f"tile{rank}.npy"), tile.reshape(part.tile_shape()))
+    np.save(os.path.join(out_dir, f"start{rank}.npy"), np.array([part.start["a"], part.start["b"]]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_partition_tiles_equal_the_undivided_result(world, tmp_path):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import imd_oracle as orc
+    port = 29500 + world + (os.getpid() % 1000)
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    A, B = _full_problem()
+    descs = []
+    for lab in ("kjbc", "kiac", "abij"):
+        e, s = _dense(lab, EXT)
+        descs.append(orc.Desc(e, s, [ord(c) for c in lab]))
+    full = orc.contract_tensor(A.reshape(-1), B.reshape(-1), np.zeros(8 * 8 * 2 * 3), *descs, 1.0, 0.0, 14)
+    full = full.reshape(8, 8, 2, 3)
+    got = np.full_like(full, np.nan)
+    for r in range(world):
+        t = np.load(tmp_path / f"tile{r}.npy")
+        a0, b0 = np.load(tmp_path / f"start{r}.npy")
+        got[a0:a0 + t.shape[0], b0:b0 + t.shape[1]] = t
+    assert np.array_equal(got.view(np.uint64), full.view(np.uint64))
+
+
+def test_partition_rejects_labels_of_the_wrong_class():
+    sys.path.insert(0, ROOT)
+    from immerdink_b200.dist import Partition
+    with pytest.raises(ValueError):
+        Partition(SPEC, EXT, 2, 0, "k", "b")
+    with pytest.raises(ValueError):
+        Partition(SPEC, dict(EXT, a=7), 2, 0, "a", "b")
