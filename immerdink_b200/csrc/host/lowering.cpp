@@ -186,6 +186,32 @@ imd_status_t lower(const imd_tensor_t& A, const imd_tensor_t& B, const imd_tenso
   return IMD_STATUS_SUCCESS;
 }
 
+const Label* find_label(const GemmView& v, int32_t id) {
+  for (const Label& l : v.labels)
+    if (l.id == id) return &l;
+  return nullptr;
+}
+
+void adopt_order(GemmView* v, int cls, const std::vector<int32_t>& order) {
+  v->order[cls] = order;
+  std::vector<Mode>& ms = v->modes[cls];
+  ms.clear();
+  for (const int32_t id : order) {
+    const Label* l = find_label(*v, id);
+    bool fuse = !ms.empty();
+    for (int x = 0; fuse && x < 3; ++x)
+      fuse = static_cast<__int128>(ms.back().stride[x]) * ms.back().extent == l->stride[x];
+    if (fuse) {
+      ms.back().extent *= l->extent;
+    } else {
+      Mode md;
+      md.extent = l->extent;
+      for (int x = 0; x < 3; ++x) md.stride[x] = l->stride[x];
+      ms.push_back(md);
+    }
+  }
+}
+
 void scatter_vector(const GemmView& v, int cls, int X, int64_t* out) {
   const int64_t size = cls == kClsI ? v.m : cls == kClsJ ? v.n : cls == kClsK ? v.k : v.b;
   const std::vector<Mode>& ms = v.modes[cls];

@@ -43,6 +43,10 @@ struct GemmView {
 imd_status_t lower(const imd_tensor_t& A, const imd_tensor_t& B, const imd_tensor_t& C,
                    GemmView* out);
 
+const Label* find_label(const GemmView& v, int32_t id);
+// Replace the canonical order of class `cls` (a permutation of its kept labels) and redo the fusion.
+void adopt_order(GemmView* v, int cls, const std::vector<int32_t>& order);
+
 // Offsets of tensor X over the fused modes of class `cls` (mixed radix, first mode fastest).
 void scatter_vector(const GemmView& v, int cls, int X, int64_t* out);
 // The nine vectors in region order: A row, k, batch; B k, col, batch; C row, col, batch.

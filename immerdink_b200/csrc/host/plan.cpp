@@ -26,7 +26,10 @@ bool product(std::initializer_list<uint64_t> xs, uint64_t* out) {
 
 uint64_t round_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
-bool workspace_layout(const GemmView& v, const imd_options_t& o, int k_align, Layout* L) {
+}  // namespace
+
+bool workspace_regions(const GemmView& v, const imd_options_t& o, int k_align, int packed_roles,
+                       Layout* L) {
   *L = Layout{};
   if (v.empty_output()) return true;
   const uint64_t m = v.m, n = v.n, k = v.k, b = v.b;
@@ -54,6 +57,8 @@ bool workspace_layout(const GemmView& v, const imd_options_t& o, int k_align, La
     bytes[IMD_REGION_VEC] = vec;
   }
   if (o.vec_mode == IMD_VEC_RESIDENT) bytes[IMD_REGION_VEC] = 0;  // plan memory instead
+  if (packed_roles & 1) bytes[IMD_REGION_SA] = bytes[IMD_REGION_FA] = bytes[IMD_REGION_RA] = 0;
+  if (packed_roles & 2) bytes[IMD_REGION_SB] = bytes[IMD_REGION_FB] = bytes[IMD_REGION_RB] = 0;
   uint64_t off = 0;
   for (int r = 0; r < IMD_REGION_COUNT; ++r) {
     if (bytes[r] == 0) continue;
@@ -66,6 +71,8 @@ bool workspace_layout(const GemmView& v, const imd_options_t& o, int k_align, La
   L->total = off;
   return true;
 }
+
+namespace {
 
 // An operand is gathered along its rows when its fastest row (or batch) mode is faster than its
 // fastest K mode; otherwise along K.
@@ -97,7 +104,7 @@ imd_status_t analyze(const imd_tensor_t* A, const imd_tensor_t* B, const imd_ten
       (v.m > INT32_MAX || v.n > INT32_MAX - 15))
     return IMD_STATUS_INVALID_VALUE;
   out->k_align = v.k > 96 ? 64 : 16;
-  if (!workspace_layout(v, out->options, out->k_align, &out->layout)) return IMD_STATUS_INVALID_VALUE;
+  if (!workspace_regions(v, out->options, out->k_align, 0, &out->layout)) return IMD_STATUS_INVALID_VALUE;
   if (out->layout.total > SIZE_MAX) return IMD_STATUS_INVALID_VALUE;
   return IMD_STATUS_SUCCESS;
 }
@@ -116,6 +123,12 @@ imd_status_t make_plan(const Analysis& an, ExecPlan* out) {
            : (an.options.mode == IMD_DIRECT || v.k == 1) ? Path::kDirect
                                                           : Path::kGemm;
   e.k_align = e.emulated() ? an.k_align : 16;
+  e.packed = an.packed.role;
+  for (int x = 0; x < 2; ++x)
+    if (e.packed & (1 << x)) {
+      for (int r = 0; r < 3; ++r) e.pack_off[x][r] = an.packed.layout[x].offset[r];
+      e.pack_bytes[x] = an.packed.layout[x].total;
+    }
   e.k_hat = (v.k + e.k_align - 1) / e.k_align * e.k_align;
   const bool rn = !e.trunc;
   *out = e;
@@ -172,7 +185,8 @@ int64_t plan_kernel_launches(const ExecPlan& e) {
   const int64_t groups = (e.N + e.g - 1) / e.g;
   // vectors; one scale launch per operand; per group one residue launch per operand and the
   // GEMM launches; one CRT launch.
-  return vec + 2 + 2 * groups + plan_gemm_launches(e) + 1;
+  const int64_t inline_ops = ((e.packed & 1) ? 0 : 1) + ((e.packed & 2) ? 0 : 1);
+  return vec + inline_ops + inline_ops * groups + plan_gemm_launches(e) + 1;
 }
 
 uint64_t plan_host_bytes(const imd_tensor_t& A, const imd_tensor_t& B, const imd_tensor_t& C,
@@ -183,6 +197,7 @@ uint64_t plan_host_bytes(const imd_tensor_t& A, const imd_tensor_t& B, const imd
   bytes += sizeof(Label) * an.view.labels.size();
   for (int g = 0; g < 4; ++g)
     bytes += 4 * an.view.order[g].size() + sizeof(Mode) * an.view.modes[g].size();
+  bytes += 8 * (an.packed.key[0].size() + an.packed.key[1].size());
   return bytes;
 }
 

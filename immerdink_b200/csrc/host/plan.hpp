@@ -26,11 +26,27 @@ struct Layout {
   uint64_t total = 0;
 };
 
+// Regions of a packed operand's buffer (shifts, flags, residue planes).
+struct PackRegions {
+  uint64_t offset[3] = {0, 0, 0}, bytes[3] = {0, 0, 0};
+  uint64_t total = 0;
+};
+
+// Which operands of a plan are read from packs, and their keys.
+struct PackedSlots {
+  int32_t caller = 0;    // bit 0 / 1: the caller's A / B
+  int32_t role = 0;      // bit 0 / 1: the post-swap A / B
+  int32_t mismatch = 0;  // IMD_PACK_MISMATCH_* of a PACK_MISMATCH status
+  std::vector<int64_t> key[2];  // by caller operand; empty = in-line
+  PackRegions layout[2];        // by post-swap role
+};
+
 struct Analysis {
   imd_options_t options{};
   GemmView view;
   int k_align = 16;
   Layout layout;
+  PackedSlots packed;
 };
 
 enum class Path : int { kNoop = 0, kGemm = 1, kDirect = 2 };
@@ -59,6 +75,9 @@ struct ExecPlan {
   uint64_t device_bytes = 0;
   bool vec_resident = false;
   int64_t k_chunks = 0;
+  int32_t packed = 0;                 // bit 0 / 1: the post-swap A / B comes from a packed buffer
+  uint64_t pack_off[2][3] = {};       // by role: offsets of shifts, flags, planes in that buffer
+  uint64_t pack_bytes[2] = {0, 0};
   ModeTable modes;
   bool emulated() const { return path == Path::kGemm && k >= 2; }
 };
@@ -67,6 +86,9 @@ IMD_INTERNAL imd_status_t analyze(const imd_tensor_t* A, const imd_tensor_t* B,
                                   const imd_tensor_t* C, const imd_options_t* options,
                                   Analysis* out);
 IMD_INTERNAL imd_status_t make_plan(const Analysis& an, ExecPlan* out);
+// The eight regions; `packed_roles` (bit 0 / 1) drops sX, fX, RX of a packed post-swap A / B.
+IMD_INTERNAL bool workspace_regions(const GemmView& v, const imd_options_t& o, int k_align,
+                                    int packed_roles, Layout* L);
 
 // K chunks of the int8 GEMM, GEMM launches and all kernel launches of one call (alpha != 0).
 IMD_INTERNAL int64_t plan_k_chunks(const ExecPlan& e);

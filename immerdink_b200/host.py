@@ -85,6 +85,27 @@ class CErr(C.Structure):
                 ("typical", C.c_double), ("unit_bound", C.c_double), ("unit_typical", C.c_double)]
 
 
+class CPackDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("num_moduli", C.c_int32), ("rounding", C.c_int32),
+                ("order", C.c_int32), ("tensor", C.POINTER(CTensor)),
+                ("num_contracted", C.c_int32), ("contracted", C.POINTER(C.c_int32)),
+                ("num_batch", C.c_int32), ("batch", C.POINTER(C.c_int32)),
+                ("num_rows", C.c_int32), ("rows", C.POINTER(C.c_int32))]
+
+
+class CPackLayout(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("status", C.c_int32), ("format", C.c_int32),
+                ("num_moduli", C.c_int32), ("rounding", C.c_int32), ("reserved", C.c_int32),
+                ("b", C.c_int64), ("r", C.c_int64), ("k", C.c_int64), ("k_hat", C.c_int64),
+                ("kappa", C.c_uint64), ("sig", CRegion), ("flag", CRegion), ("res", CRegion),
+                ("pack_bytes", C.c_uint64), ("pack_ws_bytes", C.c_uint64), ("key_digest", C.c_uint64)]
+
+
+class CPacking(C.Structure):
+    _fields_ = [("A", C.POINTER(CPackDesc)), ("B", C.POINTER(CPackDesc))]
+
+
+assert C.sizeof(CPackDesc) == 72 and C.sizeof(CPackLayout) == 136 and C.sizeof(CPacking) == 16
 assert C.sizeof(CTensor) == 32 and C.sizeof(COptions) == 24 and C.sizeof(CLowering) == 192
 assert C.sizeof(CErrRequest) == 64 and C.sizeof(CErr) == 72
 
@@ -203,6 +224,92 @@ class CDesc:
         self.t = CTensor(n, self.ext, self.st, self.lab)
 
 
+PACK_MISMATCH = ["NONE", "FORMAT", "MODULI", "ROUNDING", "CLASSES", "EXTENTS", "STRIDES", "ORDER"]
+
+
+@dataclass(frozen=True)
+class PackSpec:
+    """What to pack: the operand X and its label classes. `contracted` (K) and `batch` (L) are
+    always listed; `rows` (R) only with order "GIVEN" (every label of X listed, each class in
+    canonical order, first fastest); with "AUTO" the rest of X's labels are the rows."""
+    tensor: Desc
+    contracted: tuple
+    batch: tuple = ()
+    rows: tuple = ()
+    N: int = 14
+    rounding: str = "RN"
+    order: str = "AUTO"
+
+    def with_moduli(self, N):
+        from dataclasses import replace
+        return replace(self, N=int(N))
+
+
+class CPackSpec:
+    """Keeps the ctypes memory of one imd_pack_desc_t alive."""
+
+    def __init__(self, p):
+        self.cd = CDesc(p.tensor)
+        k, l, r = [tuple(int(x) for x in t) for t in (p.contracted, p.batch, p.rows)]
+        self.k = (C.c_int32 * max(len(k), 1))(*k)
+        self.l = (C.c_int32 * max(len(l), 1))(*l)
+        self.r = (C.c_int32 * max(len(r), 1))(*r)
+        self.d = CPackDesc(C.sizeof(CPackDesc), int(p.N), ROUNDING[p.rounding],
+                           {"AUTO": 0, "GIVEN": 1}[p.order], C.pointer(self.cd.t),
+                           len(k), self.k if k else None, len(l), self.l if l else None,
+                           len(r), self.r if r else None)
+
+
+def _packing(packing):
+    """(CPacking or None, keep-alive objects) from (PackSpec or None, PackSpec or None)."""
+    if packing is None or all(p is None for p in packing):
+        return None, None
+    keep = [None if p is None else CPackSpec(p) for p in packing]
+    cp = CPacking(None if keep[0] is None else C.pointer(keep[0].d),
+                  None if keep[1] is None else C.pointer(keep[1].d))
+    return cp, keep
+
+
+def pack_layout(spec, lib=None, check=True):
+    """Sizes and regions of the packed buffer of a PackSpec, as a dict."""
+    L = lib or load()
+    cs = CPackSpec(spec)
+    out = CPackLayout()
+    out.struct_size = C.sizeof(CPackLayout)
+    L.lib.imd_pack_layout.argtypes = [C.POINTER(CPackDesc), C.POINTER(CPackLayout)]
+    st = L.lib.imd_pack_layout(C.byref(cs.d), C.byref(out))
+    if st and check:
+        raise ImmerdinkError(st, "imd_pack_layout")
+    d = dict(status=STATUS[out.status], format=out.format, N=out.num_moduli,
+             rounding="TRUNC" if out.rounding else "RN", b=out.b, r=out.r, k=out.k, k_hat=out.k_hat,
+             kappa=out.kappa, sig=(out.sig.offset, out.sig.bytes), flag=(out.flag.offset, out.flag.bytes),
+             res=(out.res.offset, out.res.bytes), pack_bytes=out.pack_bytes,
+             pack_ws_bytes=out.pack_ws_bytes, key_digest=out.key_digest)
+    return d
+
+
+def pack_desc_for(spec, extents=None, *, operand, N, g=0, rounding="RN", mode="EMULATE",
+                  vec_mode="GENERATE", strides=None, lib=None):
+    """The GIVEN PackSpec of operand 0 (A) or 1 (B) with exactly the classes and canonical orders
+    of the unpacked plan: a pack made from it reproduces that contraction bit for bit."""
+    L, ds, o = _call(spec, extents, strides, lib, options(N, g, rounding, mode, vec_mode))
+    descs = _descs(spec, extents, strides)
+    out = CPackDesc()
+    out.struct_size = C.sizeof(CPackDesc)
+    cap = len(descs[operand].label)
+    labels = (C.c_int32 * max(cap, 1))()
+    L.lib.imd_pack_desc_for.argtypes = [C.POINTER(CTensor)] * 3 + [C.POINTER(COptions), C.c_int32,
+                                                                    C.POINTER(CPackDesc),
+                                                                    C.POINTER(C.c_int32), C.c_int32]
+    st = L.lib.imd_pack_desc_for(ds[0].t, ds[1].t, ds[2].t, o, operand, C.byref(out), labels, cap)
+    if st:
+        raise ImmerdinkError(st, "imd_pack_desc_for")
+    take = lambda ptr, n: tuple(ptr[i] for i in range(n))
+    return PackSpec(descs[operand], take(out.contracted, out.num_contracted),
+                    take(out.batch, out.num_batch), take(out.rows, out.num_rows), int(N), rounding,
+                    "GIVEN")
+
+
 def _descs(spec_or_descs, extents, strides):
     if isinstance(spec_or_descs, str):
         return contraction(spec_or_descs, extents, strides)
@@ -221,10 +328,19 @@ def _call(spec, extents, strides, lib, opt):
 
 
 def workspace_size(spec, extents=None, *, N, g=0, rounding="RN", mode="EMULATE",
-                   vec_mode="GENERATE", strides=None, lib=None):
-    """Bytes of workspace imd_contract needs for this contraction (exact)."""
+                   vec_mode="GENERATE", strides=None, packing=None, lib=None):
+    """Bytes of workspace imd_contract needs for this contraction (exact). packing = (PackSpec or
+    None, PackSpec or None): the caller's A / B read from packed buffers."""
     L, ds, o = _call(spec, extents, strides, lib, options(N, g, rounding, mode, vec_mode))
     out = C.c_size_t(0)
+    cp, keep = _packing(packing)
+    if cp is not None:
+        L.lib.imd_workspace_size_packed.argtypes = [C.POINTER(CTensor)] * 3 + [
+            C.POINTER(COptions), C.POINTER(CPacking), C.POINTER(C.c_size_t)]
+        st = L.lib.imd_workspace_size_packed(ds[0].t, ds[1].t, ds[2].t, o, C.byref(cp), C.byref(out))
+        if st:
+            raise ImmerdinkError(st, "imd_workspace_size_packed")
+        return out.value
     st = L.lib.imd_workspace_size(ds[0].t, ds[1].t, ds[2].t, o, C.byref(out))
     if st:
         raise ImmerdinkError(st, "imd_workspace_size")
@@ -258,13 +374,19 @@ def plan_bytes(spec, extents=None, *, N, g=0, rounding="RN", mode="EMULATE", vec
 
 
 def lowering(spec, extents=None, *, N, g=0, rounding="RN", mode="EMULATE", vec_mode="GENERATE",
-             strides=None, sm_count=0, lib=None, check=True):
+             strides=None, sm_count=0, packing=None, lib=None, check=True):
     """The lowering summary as a dict (status and dispatch as names)."""
     L, ds, o = _call(spec, extents, strides, lib, options(N, g, rounding, mode, vec_mode))
     out = CLowering()
     out.struct_size = C.sizeof(CLowering)
     out.sm_count = sm_count
-    st = L.lib.imd_lowering(ds[0].t, ds[1].t, ds[2].t, o, C.byref(out))
+    cp, keep = _packing(packing)
+    if cp is not None:
+        L.lib.imd_lowering_packed.argtypes = [C.POINTER(CTensor)] * 3 + [
+            C.POINTER(COptions), C.POINTER(CPacking), C.POINTER(CLowering)]
+        st = L.lib.imd_lowering_packed(ds[0].t, ds[1].t, ds[2].t, o, C.byref(cp), C.byref(out))
+    else:
+        st = L.lib.imd_lowering(ds[0].t, ds[1].t, ds[2].t, o, C.byref(out))
     if st and check:
         raise ImmerdinkError(st, "imd_lowering")
     d = {name: getattr(out, name) for name, _ in CLowering._fields_ if not name.startswith("reserved")}

@@ -212,3 +212,114 @@ def test_published_error_bounds():
         assert abs(got - want) / want < 0.02, (k, got)
     assert abs(host.err_estimate(N=12, k=16384)["bound"] - 1.95e-12) / 1.95e-12 < 0.02
     assert abs(host.err_estimate(N=16, k=16384)["bound"] - 1.6e-16) / 1.6e-16 < 0.05
+
+
+# ---------------------------------------------------------------------------- packed operands
+def _pack_queries(lib_call_desc_for, lib_call_layout, lib_call_lowering, cd, o, ds, rng):
+    """desc_for, layout and packed lowering through one library; returns a comparable record."""
+    rec = []
+    specs = []
+    for operand in (0, 1):
+        out = host.CPackDesc()
+        out.struct_size = C.sizeof(host.CPackDesc)
+        cap = max(len(ds[operand].label), 1)
+        labels = (C.c_int32 * cap)()
+        st = lib_call_desc_for(cd, o, operand, out, labels, cap)
+        lists = None
+        if st == 0:
+            lists = tuple(tuple(ptr[i] for i in range(n)) for ptr, n in
+                          ((out.contracted, out.num_contracted), (out.batch, out.num_batch),
+                           (out.rows, out.num_rows)))
+        rec.append(("desc_for", operand, st, lists))
+        specs.append(lists)
+    return rec, specs
+
+
+def _layout_record(libcall, spec):
+    cs = host.CPackSpec(spec)
+    out = host.CPackLayout()
+    out.struct_size = C.sizeof(host.CPackLayout)
+    st = libcall(C.byref(cs.d), C.byref(out))
+    fields = [getattr(out, f) for f in ("status", "format", "num_moduli", "rounding", "b", "r", "k",
+                                        "k_hat", "kappa", "pack_bytes", "pack_ws_bytes", "key_digest")]
+    regs = [(r.offset, r.bytes) for r in (out.sig, out.flag, out.res)]
+    return st, fields, regs
+
+
+@pytest.mark.skipif(REF is None, reason="reference host library not built here")
+def test_packed_queries_against_reference_host_library():
+    rng = random.Random(9)
+    same = ("status", "lowered", "dispatch", "swapped", "num_moduli", "residue_group", "num_groups",
+            "m", "n", "k", "b", "n_hat", "k_hat", "vec_entries", "kappa", "workspace_bytes",
+            "plan_device_bytes", "k_align", "packed", "pack_mismatch")
+    T, O = C.POINTER(host.CTensor), C.POINTER(host.COptions)
+    for L in (LIB.lib, REF):
+        L.imd_pack_desc_for.argtypes = [T, T, T, O, C.c_int32, C.POINTER(host.CPackDesc),
+                                        C.POINTER(C.c_int32), C.c_int32]
+        L.imd_pack_layout.argtypes = [C.POINTER(host.CPackDesc), C.POINTER(host.CPackLayout)]
+        L.imd_lowering_packed.argtypes = [T, T, T, O, C.POINTER(host.CPacking), C.POINTER(host.CLowering)]
+        L.imd_workspace_size_packed.argtypes = [T, T, T, O, C.POINTER(host.CPacking), C.POINTER(C.c_size_t)]
+    statuses = {}
+    checked = 0
+    for it in range(1500):
+        ds = random_descs(rng)
+        N = rng.randint(2, 20)
+        rounding = rng.choice(("RN", "TRUNC"))
+        o = host.options(N, rng.randint(0, N), rounding, rng.choice(("EMULATE", "EMULATE", "DIRECT")))
+        cd = [host.CDesc(d) for d in ds]
+        specs = {}
+        for name, L in (("mine", LIB.lib), ("ref", REF)):
+            got = []
+            for operand in (0, 1):
+                out = host.CPackDesc()
+                out.struct_size = C.sizeof(host.CPackDesc)
+                cap = max(len(ds[operand].label), 1)
+                labels = (C.c_int32 * cap)()
+                st = L.imd_pack_desc_for(cd[0].t, cd[1].t, cd[2].t, o, operand, C.byref(out), labels, cap)
+                lists = None
+                if st == 0:
+                    lists = tuple(tuple(ptr[i] for i in range(n)) for ptr, n in
+                                  ((out.contracted, out.num_contracted), (out.batch, out.num_batch),
+                                   (out.rows, out.num_rows)))
+                got.append((st, lists))
+            specs[name] = got
+        assert specs["mine"] == specs["ref"], (it, ds, specs)
+        if specs["mine"][0][0] != 0:
+            continue
+        # pack specs: the plan's own (GIVEN), AUTO variants, and deliberately wrong ones
+        given = [host.PackSpec(ds[x], *specs["mine"][x][1], N, rounding, "GIVEN") for x in (0, 1)]
+        variants = []
+        for x in (0, 1):
+            k, l, r = specs["mine"][x][1]
+            variants.append([given[x],
+                             host.PackSpec(ds[x], k, l, (), N, rounding, "AUTO"),
+                             host.PackSpec(ds[x], k, l, (), max(2, (N + 1) % 21), rounding, "AUTO"),
+                             host.PackSpec(ds[x], k, l, (), N, "TRUNC" if rounding == "RN" else "RN", "AUTO"),
+                             host.PackSpec(host.Desc(ds[x].extent, [s * 2 for s in ds[x].stride], ds[x].label),
+                                           k, l, (), N, rounding, "AUTO"),
+                             host.PackSpec(ds[x], tuple(reversed(k)), l, r, N, rounding, "GIVEN")])
+        for x in (0, 1):
+            for ps in variants[x]:
+                a = _layout_record(LIB.lib.imd_pack_layout, ps)
+                b = _layout_record(REF.imd_pack_layout, ps)
+                assert a == b, (it, ps, a, b)
+        for trial in range(6):
+            pa = rng.choice(variants[0] + [None])
+            pb = rng.choice(variants[1] + [None])
+            if pa is None and pb is None:
+                continue
+            cp, keep = host._packing((pa, pb))
+            mine, ref = host.CLowering(), host.CLowering()
+            mine.struct_size = ref.struct_size = 192
+            s1 = LIB.lib.imd_lowering_packed(cd[0].t, cd[1].t, cd[2].t, o, C.byref(cp), C.byref(mine))
+            s2 = REF.imd_lowering_packed(cd[0].t, cd[1].t, cd[2].t, o, C.byref(cp), C.byref(ref))
+            assert s1 == s2, (it, ds, pa, pb, s1, s2, mine.pack_mismatch, ref.pack_mismatch)
+            for f in same:
+                assert getattr(mine, f) == getattr(ref, f), (it, f, pa, pb, getattr(mine, f), getattr(ref, f))
+            b1, b2 = C.c_size_t(0), C.c_size_t(0)
+            w1 = LIB.lib.imd_workspace_size_packed(cd[0].t, cd[1].t, cd[2].t, o, C.byref(cp), C.byref(b1))
+            w2 = REF.imd_workspace_size_packed(cd[0].t, cd[1].t, cd[2].t, o, C.byref(cp), C.byref(b2))
+            assert (w1, b1.value if w1 == 0 else 0) == (w2, b2.value if w2 == 0 else 0)
+            statuses[(s1, mine.pack_mismatch)] = statuses.get((s1, mine.pack_mismatch), 0) + 1
+            checked += 1
+    assert checked > 1000 and statuses.get((0, 0), 0) > 100 and len(statuses) >= 5, statuses
