@@ -9,13 +9,18 @@
 #include <cuda_runtime_api.h>
 
 #include "immerdink/immerdink.h"
+#include "host/pack.hpp"
 #include "kernels.hpp"
 
 struct imd_handle_st {
   int device = 0;
 };
+// A pack handle: host-only (no GPU work reads it), immutable after creation.
 struct imd_pack_s {
-  int unused = 0;
+  imd::TensorCopy tensor;   // X's descriptor (aliasing interval, labels for the plan-side match)
+  imd::PackLowered pl;
+  imd::ExecPlan exec;       // the launch data of imd_pack
+  imd::ResidueTables res{};
 };
 
 namespace {
@@ -53,36 +58,26 @@ bool overlap(const Interval& x, const Interval& y) {
   return x.lo < x.hi && y.lo < y.hi && x.lo < y.hi && y.lo < x.hi;
 }
 
-}  // namespace
-
-extern "C" {
-
-imd_status_t imd_create(imd_handle_t* handle) {
-  if (handle == nullptr) return IMD_STATUS_INVALID_VALUE;
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) {
-    cudaGetLastError();
-    return IMD_STATUS_CUDA_ERROR;
-  }
-  auto* h = new (std::nothrow) imd_handle_st{device};
-  if (h == nullptr) return IMD_STATUS_ALLOC_FAILED;
-  *handle = h;
-  return IMD_STATUS_SUCCESS;
-}
-
-imd_status_t imd_destroy(imd_handle_t handle) {
-  delete handle;
-  return IMD_STATUS_SUCCESS;
-}
-
-imd_status_t imd_plan_create(imd_handle_t handle, const imd_tensor_t* A, const imd_tensor_t* B,
-                             const imd_tensor_t* C, const imd_options_t* options,
-                             imd_plan_t* plan) {
+imd_status_t plan_create(imd_handle_t handle, const imd_tensor_t* A, const imd_tensor_t* B,
+                         const imd_tensor_t* C, const imd_options_t* options,
+                         const imd_pack_t pack[2], imd_plan_t* plan) {
   if (handle == nullptr || plan == nullptr) return IMD_STATUS_INVALID_VALUE;
   try {
     imd::Analysis an;
     if (const imd_status_t st = imd::analyze(A, B, C, options, &an); st != IMD_STATUS_SUCCESS)
       return st;
+    if (pack[0] != nullptr || pack[1] != nullptr) {
+      imd::PackSource ps[2];
+      const imd::PackSource* src[2] = {nullptr, nullptr};
+      for (int x = 0; x < 2; ++x) {
+        if (pack[x] == nullptr) continue;
+        ps[x] = imd::PackSource{static_cast<int32_t>(pack[x]->tensor.label.size()),
+                                pack[x]->tensor.label.data(), &pack[x]->pl};
+        src[x] = &ps[x];
+      }
+      if (const imd_status_t st = imd::match_packs(A, B, src, &an); st != IMD_STATUS_SUCCESS)
+        return st;
+    }
     imd::ExecPlan e;
     if (const imd_status_t st = imd::make_plan(an, &e); st != IMD_STATUS_SUCCESS) return st;
     auto p = std::make_unique<imd_plan_st>();
@@ -90,6 +85,7 @@ imd_status_t imd_plan_create(imd_handle_t handle, const imd_tensor_t* A, const i
     p->view = an.view;
     p->A = imd::TensorCopy(*A), p->B = imd::TensorCopy(*B), p->C = imd::TensorCopy(*C);
     p->exec = e;
+    for (int x = 0; x < 2; ++x) p->slot_key[x] = an.packed.key[x];
     p->crt = imd::crt_tables(e.N);
     p->res = imd::residue_tables(e.N);
     if (e.path != imd::Path::kNoop) {
@@ -130,6 +126,35 @@ imd_status_t imd_plan_create(imd_handle_t handle, const imd_tensor_t* A, const i
   }
 }
 
+}  // namespace
+
+extern "C" {
+
+imd_status_t imd_create(imd_handle_t* handle) {
+  if (handle == nullptr) return IMD_STATUS_INVALID_VALUE;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
+  auto* h = new (std::nothrow) imd_handle_st{device};
+  if (h == nullptr) return IMD_STATUS_ALLOC_FAILED;
+  *handle = h;
+  return IMD_STATUS_SUCCESS;
+}
+
+imd_status_t imd_destroy(imd_handle_t handle) {
+  delete handle;
+  return IMD_STATUS_SUCCESS;
+}
+
+imd_status_t imd_plan_create(imd_handle_t handle, const imd_tensor_t* A, const imd_tensor_t* B,
+                             const imd_tensor_t* C, const imd_options_t* options,
+                             imd_plan_t* plan) {
+  const imd_pack_t none[2] = {nullptr, nullptr};
+  return plan_create(handle, A, B, C, options, none, plan);
+}
+
 imd_status_t imd_plan_destroy(imd_plan_t plan) {
   if (plan != nullptr && plan->vec_dev != nullptr) cudaFree(plan->vec_dev);
   delete plan;
@@ -168,35 +193,122 @@ imd_status_t imd_contract(imd_plan_t plan, double alpha, const double* A, const 
   }
 }
 
-/* ---- packed operands: not available yet; the entry points exist and refuse ----------------- */
+/* ---- packed operands (ref: src/api.cpp:211-276 and :336-394) ---------------------------------- */
 imd_status_t imd_pack_create(imd_handle_t handle, const imd_pack_desc_t* desc, imd_pack_t* pack) {
   if (handle == nullptr || desc == nullptr || pack == nullptr) return IMD_STATUS_INVALID_VALUE;
-  return IMD_STATUS_NOT_SUPPORTED;
+  try {
+    imd::PackLowered pl;
+    if (const imd_status_t st = imd::pack_lower(*desc, &pl); st != IMD_STATUS_SUCCESS) return st;
+    auto p = std::make_unique<imd_pack_s>();
+    p->tensor = imd::TensorCopy(*desc->tensor);
+    p->pl = std::move(pl);
+    imd::pack_exec(p->pl, &p->exec);
+    p->res = imd::residue_tables(p->pl.N);
+    *pack = p.release();
+    return IMD_STATUS_SUCCESS;
+  } catch (const std::bad_alloc&) {
+    return IMD_STATUS_ALLOC_FAILED;
+  } catch (...) {
+    return IMD_STATUS_INVALID_VALUE;
+  }
 }
+
 imd_status_t imd_pack_destroy(imd_pack_t pack) {
   delete pack;
   return IMD_STATUS_SUCCESS;
 }
-imd_status_t imd_pack_bytes(imd_pack_t pack, size_t*, size_t*) {
-  return pack == nullptr ? IMD_STATUS_INVALID_VALUE : IMD_STATUS_NOT_SUPPORTED;
+
+imd_status_t imd_pack_bytes(imd_pack_t pack, size_t* pack_bytes, size_t* pack_ws_bytes) {
+  if (pack == nullptr) return IMD_STATUS_INVALID_VALUE;
+  if (pack_bytes != nullptr) *pack_bytes = static_cast<size_t>(pack->pl.layout.total);
+  if (pack_ws_bytes != nullptr) *pack_ws_bytes = static_cast<size_t>(pack->pl.ws_bytes);
+  return IMD_STATUS_SUCCESS;
 }
-imd_status_t imd_pack(imd_pack_t pack, const double*, void*, size_t, void*, size_t, cudaStream_t) {
-  return pack == nullptr ? IMD_STATUS_INVALID_VALUE : IMD_STATUS_NOT_SUPPORTED;
+
+imd_status_t imd_pack(imd_pack_t pack, const double* X, void* packed, size_t packed_bytes,
+                      void* ws, size_t ws_bytes, cudaStream_t stream) {
+  // order: null pointers; an empty pack; ALIASING; MISALIGNED; sizes
+  if (pack == nullptr) return IMD_STATUS_INVALID_VALUE;
+  const uint64_t need = pack->pl.layout.total, need_ws = pack->pl.ws_bytes;
+  if ((need > 0 && (X == nullptr || packed == nullptr)) || (need_ws > 0 && ws == nullptr))
+    return IMD_STATUS_INVALID_VALUE;
+  if (need == 0) return IMD_STATUS_SUCCESS;
+  const Interval iX = tensor_bytes(pack->tensor, X), iP = raw_bytes(packed, need),
+                 iW = raw_bytes(ws, need_ws);
+  if (overlap(iP, iX) || overlap(iW, iX) || overlap(iW, iP)) return IMD_STATUS_ALIASING;
+  if (!aligned(X, 8) || !aligned(packed, imd::kRegionAlign) ||
+      (need_ws > 0 && !aligned(ws, imd::kRegionAlign)))
+    return IMD_STATUS_MISALIGNED;
+  if (packed_bytes < need || ws_bytes < need_ws) return IMD_STATUS_INSUFFICIENT_WORKSPACE;
+  try {
+    return imd::enqueue_pack(pack->exec, pack->res, pack->pl.layout, X, packed, ws, stream);
+  } catch (...) {
+    return IMD_STATUS_CUDA_ERROR;
+  }
 }
+
 imd_status_t imd_plan_create_packed(imd_handle_t handle, const imd_tensor_t* A,
                                     const imd_tensor_t* B, const imd_tensor_t* C,
                                     const imd_options_t* options, imd_pack_t packA,
                                     imd_pack_t packB, imd_plan_t* plan) {
-  if (packA == nullptr && packB == nullptr) return imd_plan_create(handle, A, B, C, options, plan);
-  return IMD_STATUS_NOT_SUPPORTED;
+  const imd_pack_t packs[2] = {packA, packB};
+  return plan_create(handle, A, B, C, options, packs, plan);
 }
+
 imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operand_t* A,
                                  const imd_operand_t* B, double beta, double* C, void* ws,
                                  size_t ws_bytes, cudaStream_t stream) {
+  // order: operands and packed slots; null pointers; empty output; ALIASING; MISALIGNED; sizes
   if (plan == nullptr || A == nullptr || B == nullptr) return IMD_STATUS_INVALID_VALUE;
-  if (A->packed != nullptr || A->pack != nullptr || B->packed != nullptr || B->pack != nullptr)
-    return IMD_STATUS_PACK_MISMATCH;
-  return imd_contract(plan, alpha, A->data, B->data, beta, C, ws, ws_bytes, stream);
+  const imd::ExecPlan& e = plan->exec;
+  const imd_operand_t* op[2] = {A, B};
+  int role[2];  // post-swap role of the caller's operand x
+  for (int x = 0; x < 2; ++x) {
+    role[x] = (x == 0) != e.swapped ? 0 : 1;
+    if (plan->slot_key[x].empty()) {
+      if (op[x]->packed != nullptr || op[x]->pack != nullptr) return IMD_STATUS_PACK_MISMATCH;
+    } else if (op[x]->pack == nullptr || op[x]->pack->pl.key != plan->slot_key[x]) {
+      return IMD_STATUS_PACK_MISMATCH;
+    }
+  }
+  const bool reads_ab = alpha != 0.0 && e.k != 0;
+  const bool reads_pack = reads_ab && e.emulated();
+  const uint64_t need = e.layout.total;
+  if (C == nullptr || (reads_ab && (A->data == nullptr || B->data == nullptr)) ||
+      (need > 0 && ws == nullptr))
+    return IMD_STATUS_INVALID_VALUE;
+  for (int x = 0; x < 2; ++x)
+    if (!plan->slot_key[x].empty() && reads_pack && e.pack_bytes[role[x]] > 0 &&
+        op[x]->packed == nullptr)
+      return IMD_STATUS_INVALID_VALUE;
+  if (e.path == imd::Path::kNoop) return IMD_STATUS_SUCCESS;
+  // C against every input range; the workspace against those and C. Packed buffers may overlap
+  // each other and the FP64 operands: all are only read.
+  const Interval iC = tensor_bytes(plan->C, C), iW = raw_bytes(ws, need);
+  Interval in[4] = {tensor_bytes(plan->A, A->data), tensor_bytes(plan->B, B->data), {}, {}};
+  for (int x = 0; x < 2; ++x)
+    if (!plan->slot_key[x].empty()) in[2 + x] = raw_bytes(op[x]->packed, e.pack_bytes[role[x]]);
+  if (overlap(iW, iC)) return IMD_STATUS_ALIASING;
+  for (const Interval& r : in)
+    if (overlap(iC, r) || overlap(iW, r)) return IMD_STATUS_ALIASING;
+  if (!aligned(A->data, 8) || !aligned(B->data, 8) || !aligned(C, 8) ||
+      !aligned(A->packed, imd::kRegionAlign) || !aligned(B->packed, imd::kRegionAlign) ||
+      (need > 0 && !aligned(ws, imd::kRegionAlign)))
+    return IMD_STATUS_MISALIGNED;
+  if (ws_bytes < need) return IMD_STATUS_INSUFFICIENT_WORKSPACE;
+  for (int x = 0; x < 2; ++x)
+    if (op[x]->packed != nullptr && op[x]->packed_bytes < e.pack_bytes[role[x]])
+      return IMD_STATUS_INSUFFICIENT_WORKSPACE;
+  const double* gA = e.swapped ? B->data : A->data;
+  const double* gB = e.swapped ? A->data : B->data;
+  const void* packed[2] = {nullptr, nullptr};  // by post-swap role
+  for (int x = 0; x < 2; ++x)
+    if (!plan->slot_key[x].empty()) packed[role[x]] = op[x]->packed;
+  try {
+    return imd::enqueue_contract(*plan, alpha, gA, gB, beta, C, ws, stream, packed);
+  } catch (...) {
+    return IMD_STATUS_CUDA_ERROR;
+  }
 }
 
 /* ---- verification hooks (not part of the drop-in ABI) ---------------------------------------- */

@@ -711,7 +711,7 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
   const bool pair = variant == 2 || (variant == 0 && s.m > kTileM);
   CUtensorMap map_a, map_b;
   if (!encode_planes(fn, &map_a, RA, s.k_hat, s.m, s.planes, kTileM) ||
-      !encode_planes(fn, &map_b, RB, s.k_hat, s.n_hat, s.planes, pair ? 128 : kTileN))
+      !encode_planes(fn, &map_b, RB, s.k_hat, s.b_rows, s.planes, pair ? 128 : kTileN))
     return IMD_STATUS_CUDA_ERROR;
   GemmParams p{};
   p.s = s;

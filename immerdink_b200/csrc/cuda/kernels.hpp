@@ -17,7 +17,8 @@ namespace imd {
 // into the product planes starting at modulus mod0. A product plane holds
 // y = (q_l * sum_h RA RB) mod p_l, the form the CRT consumes.
 struct GemmShape {
-  int32_t m, n_hat;        // rows of A per plane; padded rows of B per plane (= W row pitch)
+  int32_t m, n_hat;        // rows of A per plane; row pitch of W (columns of C, padded to 16)
+  int32_t b_rows;          // rows of B per plane: n_hat in the workspace, n in a packed buffer
   int32_t k_hat;           // row pitch of the residue planes (bytes)
   int32_t k0, klen;        // K chunk
   int32_t planes;          // slots x batches in this launch
@@ -45,9 +46,13 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
 imd_status_t gemm_reference_launch(const GemmShape& s, const int8_t* RA, const int8_t* RB,
                                    uint8_t* W, cudaStream_t stream);
 
+// `packed[x]`: the packed buffer of the post-swap operand x of a plan with that slot packed.
 imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
                               const double* B, double beta, double* C, void* ws,
-                              cudaStream_t stream);
+                              cudaStream_t stream, const void* const packed[2] = nullptr);
+// imd_pack: shifts, flags and all N residue planes of X into `packed` (every byte written).
+imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const PackRegions& layout,
+                          const double* X, void* packed, void* ws, cudaStream_t stream);
 imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stream);
 
 // Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.

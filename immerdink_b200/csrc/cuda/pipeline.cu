@@ -32,6 +32,7 @@ constexpr int kThreads = 256;
 struct VecParams {
   ModeTable modes;
   int64_t m, n, k, b;
+  int32_t segments;  // 9: all vectors of a contraction; 3: rows, K and batches of operand A only
 };
 
 __device__ __forceinline__ int64_t radix_offset(const ModeTable& t, int cls, int X, int64_t q) {
@@ -48,7 +49,7 @@ __device__ __forceinline__ int64_t radix_offset(const ModeTable& t, int cls, int
 
 __global__ void __launch_bounds__(kThreads) k_vectors(const __grid_constant__ VecParams p,
                                                       int64_t* __restrict__ vec) {
-  const int64_t total = 2 * p.m + 2 * p.n + 2 * p.k + 3 * p.b;
+  const int64_t total = p.segments == 3 ? p.m + p.k + p.b : 2 * p.m + 2 * p.n + 2 * p.k + 3 * p.b;
   const int64_t seg[9] = {p.m, p.k, p.b, p.k, p.n, p.b, p.m, p.n, p.b};
   const int cls[9] = {kClsI, kClsK, kClsL, kClsK, kClsJ, kClsL, kClsI, kClsJ, kClsL};
   const int ten[9] = {kTenA, kTenA, kTenA, kTenB, kTenB, kTenB, kTenC, kTenC, kTenC};
@@ -503,9 +504,9 @@ __global__ void __launch_bounds__(kThreads) k_gemm_reference(const __grid_consta
   const int64_t i = rem / s.n_hat, j = rem % s.n_hat;
   const int slot = static_cast<int>(z / s.batches);
   const int8_t* a = RA + (z * s.m + i) * static_cast<int64_t>(s.k_hat) + s.k0;
-  const int8_t* b = RB + (z * s.n_hat + j) * static_cast<int64_t>(s.k_hat) + s.k0;
+  const int8_t* b = RB + (z * s.b_rows + j) * static_cast<int64_t>(s.k_hat) + s.k0;
   int acc = 0;
-  for (int h = 0; h < s.klen; h += 4)
+  for (int h = 0; h < s.klen && j < s.b_rows; h += 4)
     acc = __dp4a(*reinterpret_cast<const int*>(a + h), *reinterpret_cast<const int*>(b + h), acc);
   uint8_t* w = W + ((static_cast<int64_t>(s.mod0 + slot) * s.batches + z % s.batches) * s.m + i) * s.n_hat + j;
   const int64_t pm = s.p[slot];
@@ -545,6 +546,7 @@ imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stre
   VecParams p;
   p.modes = e.modes;
   p.m = e.m, p.n = e.n, p.k = e.k, p.b = e.b;
+  p.segments = 9;
   k_vectors<<<grid_for(e.vec_count, 1 << 20), kThreads, 0, stream>>>(p, vec);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
@@ -560,6 +562,7 @@ GemmShape gemm_shape(const ExecPlan& e, const uint32_t* crt_q, int mod0, int mod
   GemmShape s{};
   s.m = static_cast<int32_t>(e.m);
   s.n_hat = static_cast<int32_t>(e.n_hat);
+  s.b_rows = static_cast<int32_t>((e.packed & 2) ? e.n : e.n_hat);
   s.k_hat = static_cast<int32_t>(e.k_hat);
   s.k0 = static_cast<int32_t>(chunk * kChunk);
   s.klen = static_cast<int32_t>(e.k_hat - s.k0 < kChunk ? e.k_hat - s.k0 : kChunk);
@@ -630,9 +633,89 @@ int profile_read(float* ms_by_tag, int tags) {
   return n;
 }
 
+namespace {
+
+// One post-swap operand as the scale and residue kernels read it.
+struct OperandView {
+  const double* X;
+  const int64_t *row, *kv, *bat;
+  int64_t rows, rows_pad;  // rows per batch; rows per batch of the residue planes
+  bool rows_fast;
+  int64_t k_run;
+};
+
+OperandView operand_view(const ExecPlan& e, const Vectors& v, int x, const double* X) {
+  OperandView o;
+  o.X = X;
+  o.row = x == 0 ? v.a_row : v.b_col;
+  o.kv = x == 0 ? v.a_k : v.b_k;
+  o.bat = x == 0 ? v.a_bat : v.b_bat;
+  o.rows = x == 0 ? e.m : e.n;
+  o.rows_pad = x == 0 ? e.m : e.n_hat;
+  o.rows_fast = e.rows_fast[x];
+  o.k_run = e.modes.count[kClsK] > 0 && e.modes.stride[e.modes.first[kClsK]][x] == 1
+                ? e.modes.extent[e.modes.first[kClsK]]
+                : 0;
+  return o;
+}
+
+bool launch_scale(const ExecPlan& e, const OperandView& o, int16_t* sigma, uint8_t* flag,
+                  cudaStream_t stream) {
+  ScaleParams p{};
+  p.X = o.X;
+  p.row = o.row, p.kv = o.kv, p.bat = o.bat;
+  p.rows = o.rows;
+  p.batches = e.b;
+  p.k = e.k;
+  p.rows_fast = o.rows_fast;
+  p.lg_rt = scale_lg_rt(o.rows_fast, e.k);
+  p.lhs_shift = e.lhs_shift;
+  p.rhs = e.rhs;
+  p.sigma = sigma;
+  p.flag = flag;
+  const int64_t rt = int64_t{1} << p.lg_rt;
+  const int64_t blocks = (p.rows * p.batches + rt - 1) / rt;
+  k_scale<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(p);
+  return launched();
+}
+
+// Residue planes of moduli [mod0, mod0 + mods) of one operand into R[slot][batch][rows_pad][k_hat].
+bool launch_residues(const ExecPlan& e, const ResidueTables& t, const OperandView& o,
+                     const int16_t* sigma, int8_t* R, int mod0, int mods, cudaStream_t stream) {
+  ResidueParams p{};
+  p.X = o.X;
+  p.row = o.row, p.kv = o.kv, p.bat = o.bat;
+  p.rows = o.rows;
+  p.rows_pad = o.rows_pad;
+  p.batches = e.b;
+  p.k = e.k;
+  p.k_hat = e.k_hat;
+  p.rows_fast = o.rows_fast;
+  p.k_run = o.k_run;
+  p.trunc = e.trunc;
+  p.mod0 = mod0;
+  p.mods = mods;
+  p.sigma = sigma;
+  p.R = R;
+  p.t = t;
+  const int64_t fast_n = p.rows_fast ? p.rows_pad * p.batches : (p.k_hat >> 4);
+  const int64_t slow_n = p.rows_fast ? (p.k_hat >> 4) : p.rows_pad * p.batches;
+  p.lg_fast = 0;
+  while (p.lg_fast < 8 && (int64_t{1} << p.lg_fast) < fast_n) ++p.lg_fast;
+  const int64_t F = int64_t{1} << p.lg_fast, per = kThreads / F;
+  const int64_t gy = (slow_n + per - 1) / per;
+  const dim3 grid(static_cast<unsigned int>((fast_n + F - 1) / F),
+                  static_cast<unsigned int>(gy < 65535 ? gy : 65535));
+  if (t.words == 2) k_residues<2><<<grid, kThreads, 0, stream>>>(p);
+  else k_residues<3><<<grid, kThreads, 0, stream>>>(p);
+  return launched();
+}
+
+}  // namespace
+
 imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
                               const double* B, double beta, double* C, void* ws,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, const void* const packed[2]) {
   const ExecPlan& e = plan.exec;
   char* base = static_cast<char*>(ws);
   auto region = [&](int r) { return base + e.layout.offset[r]; };
@@ -653,81 +736,61 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
   }
 
-  int16_t* sA = reinterpret_cast<int16_t*>(region(IMD_REGION_SA));
-  int16_t* sB = reinterpret_cast<int16_t*>(region(IMD_REGION_SB));
-  uint8_t* fA = reinterpret_cast<uint8_t*>(region(IMD_REGION_FA));
-  uint8_t* fB = reinterpret_cast<uint8_t*>(region(IMD_REGION_FB));
-  int8_t* RA = reinterpret_cast<int8_t*>(region(IMD_REGION_RA));
-  int8_t* RB = reinterpret_cast<int8_t*>(region(IMD_REGION_RB));
-  uint8_t* W = reinterpret_cast<uint8_t*>(region(IMD_REGION_W));
-
+  const void* const no_packs[2] = {nullptr, nullptr};
+  if (packed == nullptr) packed = no_packs;
+  // shifts, flags and residue planes of each post-swap operand: workspace regions, or the regions
+  // of its packed buffer (then nothing is computed for that operand here)
+  const int16_t* sX[2];
+  const uint8_t* fX[2];
+  const int8_t* RX[2];
+  const int sreg[2] = {IMD_REGION_SA, IMD_REGION_SB}, freg[2] = {IMD_REGION_FA, IMD_REGION_FB},
+            rreg[2] = {IMD_REGION_RA, IMD_REGION_RB};
+  bool from_pack[2];
   for (int x = 0; x < 2; ++x) {
-    ScaleParams p{};
-    p.X = x == 0 ? A : B;
-    p.row = x == 0 ? v.a_row : v.b_col;
-    p.kv = x == 0 ? v.a_k : v.b_k;
-    p.bat = x == 0 ? v.a_bat : v.b_bat;
-    p.rows = x == 0 ? e.m : e.n;
-    p.batches = e.b;
-    p.k = e.k;
-    p.rows_fast = e.rows_fast[x];
-    p.lg_rt = scale_lg_rt(e.rows_fast[x], e.k);
-    p.lhs_shift = e.lhs_shift;
-    p.rhs = e.rhs;
-    p.sigma = x == 0 ? sA : sB;
-    p.flag = x == 0 ? fA : fB;
-    const int64_t rt = int64_t{1} << p.lg_rt;
-    const int64_t blocks = (p.rows * p.batches + rt - 1) / rt;
-    k_scale<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(p);
-    if (!launched()) return IMD_STATUS_CUDA_ERROR;
+    from_pack[x] = (e.packed >> x) & 1;
+    if (from_pack[x]) {
+      if (packed[x] == nullptr) return IMD_STATUS_INVALID_VALUE;
+      const char* pk = static_cast<const char*>(packed[x]);
+      sX[x] = reinterpret_cast<const int16_t*>(pk + e.pack_off[x][0]);
+      fX[x] = reinterpret_cast<const uint8_t*>(pk + e.pack_off[x][1]);
+      RX[x] = reinterpret_cast<const int8_t*>(pk + e.pack_off[x][2]);
+    } else {
+      sX[x] = reinterpret_cast<const int16_t*>(region(sreg[x]));
+      fX[x] = reinterpret_cast<const uint8_t*>(region(freg[x]));
+      RX[x] = reinterpret_cast<const int8_t*>(region(rreg[x]));
+    }
   }
+  uint8_t* W = reinterpret_cast<uint8_t*>(region(IMD_REGION_W));
+  const OperandView ov[2] = {operand_view(e, v, 0, A), operand_view(e, v, 1, B)};
+
+  for (int x = 0; x < 2; ++x)
+    if (!from_pack[x] &&
+        !launch_scale(e, ov[x], const_cast<int16_t*>(sX[x]), const_cast<uint8_t*>(fX[x]), stream))
+      return IMD_STATUS_CUDA_ERROR;
 
   mark(1, stream);
-  const ResidueTables& rt = plan.res;
   GemmPlanInfo info;
   info.encode_tiled = plan.encode_tiled;
   info.error_word = static_cast<unsigned int*>(plan.error_word);
   info.sms = plan.sms;
   for (int g0 = 0; g0 < e.N; g0 += e.g) {
     const int mods = e.N - g0 < e.g ? e.N - g0 : e.g;
+    const int8_t* Rg[2];
     for (int x = 0; x < 2; ++x) {
-      ResidueParams p{};
-      p.X = x == 0 ? A : B;
-      p.row = x == 0 ? v.a_row : v.b_col;
-      p.kv = x == 0 ? v.a_k : v.b_k;
-      p.bat = x == 0 ? v.a_bat : v.b_bat;
-      p.rows = x == 0 ? e.m : e.n;
-      p.rows_pad = x == 0 ? e.m : e.n_hat;
-      p.batches = e.b;
-      p.k = e.k;
-      p.k_hat = e.k_hat;
-      p.rows_fast = e.rows_fast[x];
-      p.k_run = e.modes.count[kClsK] > 0 && e.modes.stride[e.modes.first[kClsK]][x] == 1
-                    ? e.modes.extent[e.modes.first[kClsK]]
-                    : 0;
-      p.trunc = e.trunc;
-      p.mod0 = g0;
-      p.mods = mods;
-      p.sigma = x == 0 ? sA : sB;
-      p.R = x == 0 ? RA : RB;
-      p.t = rt;
-      const int64_t fast_n = p.rows_fast ? p.rows_pad * p.batches : (p.k_hat >> 4);
-      const int64_t slow_n = p.rows_fast ? (p.k_hat >> 4) : p.rows_pad * p.batches;
-      p.lg_fast = 0;
-      while (p.lg_fast < 8 && (int64_t{1} << p.lg_fast) < fast_n) ++p.lg_fast;
-      const int64_t F = int64_t{1} << p.lg_fast, per = kThreads / F;
-      const int64_t gy = (slow_n + per - 1) / per;
-      const dim3 grid(static_cast<unsigned int>((fast_n + F - 1) / F),
-                      static_cast<unsigned int>(gy < 65535 ? gy : 65535));
-      if (rt.words == 2) k_residues<2><<<grid, kThreads, 0, stream>>>(p);
-      else k_residues<3><<<grid, kThreads, 0, stream>>>(p);
-      if (!launched()) return IMD_STATUS_CUDA_ERROR;
+      if (from_pack[x]) {  // a packed buffer holds all N planes: the group's start at plane g0
+        Rg[x] = RX[x] + static_cast<int64_t>(g0) * e.b * ov[x].rows * e.k_hat;
+        continue;
+      }
+      Rg[x] = RX[x];
+      if (!launch_residues(e, plan.res, ov[x], sX[x], const_cast<int8_t*>(RX[x]), g0, mods, stream))
+        return IMD_STATUS_CUDA_ERROR;
     }
     mark(2, stream);
     for (int64_t c = 0; c < e.k_chunks; ++c) {
       const GemmShape s = gemm_shape(e, plan.crt.q, g0, mods, static_cast<int>(c));
-      const imd_status_t st = use_reference_gemm() ? gemm_reference_launch(s, RA, RB, W, stream)
-                                                   : gemm_launch(info, s, RA, RB, W, stream);
+      const imd_status_t st = use_reference_gemm()
+                                  ? gemm_reference_launch(s, Rg[0], Rg[1], W, stream)
+                                  : gemm_launch(info, s, Rg[0], Rg[1], W, stream);
       if (st != IMD_STATUS_SUCCESS) return st;
     }
     mark(3, stream);
@@ -735,7 +798,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
 
   CrtParams p{};
   p.W = W;
-  p.sigma = sA, p.tau = sB, p.fA = fA, p.fB = fB;
+  p.sigma = sX[0], p.tau = sX[1], p.fA = fX[0], p.fB = fX[1];
   p.A = A, p.B = B, p.C = C;
   p.v = v;
   p.m = e.m, p.n = e.n, p.n_hat = e.n_hat, p.k = e.k, p.b = e.b;
@@ -760,6 +823,69 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   }
   mark(4, stream);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+// ---- imd_pack --------------------------------------------------------------------------------
+namespace {
+
+struct ZeroRanges {
+  uint64_t begin[4], end[4];
+};
+
+// The bytes of a packed buffer that no row owns: the alignment gaps behind each region and the
+// tail behind the last residue plane. A few hundred bytes plus at most 15 rows of k_hat.
+__global__ void __launch_bounds__(kThreads) k_zero_ranges(const __grid_constant__ ZeroRanges z,
+                                                          uint8_t* __restrict__ out) {
+  for (int r = 0; r < 4; ++r)
+    for (uint64_t at = z.begin[r] + blockIdx.x * static_cast<uint64_t>(kThreads) + threadIdx.x;
+         at < z.end[r]; at += static_cast<uint64_t>(gridDim.x) * kThreads)
+      out[at] = 0;
+}
+
+}  // namespace
+
+imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const PackRegions& layout,
+                          const double* X, void* packed, void* ws, cudaStream_t stream) {
+  if (layout.total == 0) return IMD_STATUS_SUCCESS;
+  uint8_t* out = static_cast<uint8_t*>(packed);
+  int64_t* vec = static_cast<int64_t*>(ws);
+  VecParams vp;
+  vp.modes = e.modes;
+  vp.m = e.m, vp.n = 0, vp.k = e.k, vp.b = e.b;
+  vp.segments = 3;
+  k_vectors<<<grid_for(e.vec_count, 1 << 20), kThreads, 0, stream>>>(vp, vec);
+  if (!launched()) return IMD_STATUS_CUDA_ERROR;
+
+  const uint64_t planes = static_cast<uint64_t>(e.N) * e.b * e.m * e.k_hat;
+  ZeroRanges z{};
+  uint64_t longest = 0;
+  for (int r = 0; r < 3; ++r) {
+    z.begin[r] = layout.offset[r] + layout.bytes[r];
+    z.end[r] = r < 2 ? layout.offset[r + 1] : layout.total;
+  }
+  z.begin[3] = layout.offset[2] + planes;          // the tail: part of region 2's byte count
+  z.end[3] = layout.offset[2] + layout.bytes[2];
+  for (int r = 0; r < 4; ++r)
+    if (z.end[r] - z.begin[r] > longest) longest = z.end[r] - z.begin[r];
+  if (longest > 0) {
+    k_zero_ranges<<<grid_for(static_cast<int64_t>(longest), 1 << 16), kThreads, 0, stream>>>(z, out);
+    if (!launched()) return IMD_STATUS_CUDA_ERROR;
+  }
+
+  OperandView o;  // X as operand A of a one-operand view: rows, K, batches
+  o.X = X;
+  o.row = vec, o.kv = vec + e.m, o.bat = vec + e.m + e.k;
+  o.rows = e.m, o.rows_pad = e.m;
+  o.rows_fast = e.rows_fast[0];
+  o.k_run = e.modes.count[kClsK] > 0 && e.modes.stride[e.modes.first[kClsK]][kTenA] == 1
+                ? e.modes.extent[e.modes.first[kClsK]]
+                : 0;
+  int16_t* sigma = reinterpret_cast<int16_t*>(out + layout.offset[0]);
+  if (!launch_scale(e, o, sigma, out + layout.offset[1], stream)) return IMD_STATUS_CUDA_ERROR;
+  if (!launch_residues(e, tables, o, sigma, reinterpret_cast<int8_t*>(out + layout.offset[2]), 0,
+                       e.N, stream))
+    return IMD_STATUS_CUDA_ERROR;
+  return IMD_STATUS_SUCCESS;
 }
 
 // ---- built-in workspace ---------------------------------------------------------------------------

@@ -161,6 +161,207 @@ def default_handle(lib=None):
         return _handles[key]
 
 
+def pack_spec(spec, A, B, C, *, operand, N, g=0, rounding="RN", mode="EMULATE",
+              vec_mode="GENERATE", lib=None):
+    """imd_pack_desc_for: the GIVEN host.PackSpec of operand 0 (A) or 1 (B) with the classes and
+    orders the unpacked plan uses (a pack of it reproduces that contraction bit for bit).
+    A, B, C: arrays or Layouts. (ref: python/immerdink/device.py:289-296)"""
+    descs = _descs(spec, [_layout(x, n) for x, n in zip((A, B, C), "ABC")])
+    return host.pack_desc_for(descs, operand=operand, N=N, g=g, rounding=rounding, mode=mode,
+                              vec_mode=vec_mode, lib=load_library(lib).host)
+
+
+class PackRecord(namedtuple("PackRecord", "N rounding pack_bytes key_digest")):
+    """What a PackedBuffer remembers: N, rounding, pack_bytes and the key digest of a pack."""
+    __slots__ = ()
+
+
+class Pack:
+    """imd_pack_create of a host.PackSpec: an immutable host object (key and layout).
+    `.pack(X, out)` writes the packed operand into caller-owned device memory of `pack_bytes`
+    bytes. (ref: python/immerdink/device.py:299-413)"""
+
+    def __init__(self, spec, *, handle=None, lib=None):
+        self.lib = load_library(lib if handle is None else handle.lib)
+        self.handle = handle or default_handle(self.lib)
+        self.spec = spec
+        self._cd = host.CPackSpec(spec)
+        h = ct.c_void_p()
+        L = self.lib.lib
+        st = L.imd_pack_create(self.handle._h, ct.byref(self._cd.d), ct.byref(h))
+        if st:
+            raise _error(st, "imd_pack_create")
+        self._h = h.value
+        self._fin = weakref.finalize(self, L.imd_pack_destroy, h.value)
+        pb, wb = ct.c_size_t(0), ct.c_size_t(0)
+        st = L.imd_pack_bytes(self._h, ct.byref(pb), ct.byref(wb))
+        if st:
+            raise _error(st, "imd_pack_bytes")
+        self.pack_bytes, self.workspace_bytes = pb.value, wb.value
+        self._x = _Expected(spec.tensor, "X")
+        self._fn = L.imd_pack
+        self._layout = self._rec = None
+        self._lock = threading.Lock()
+        self._users = 0      # open plans made with this pack: they keep passing its handle
+        self.closed = False
+
+    def _acquire(self):
+        with self._lock:
+            if self.closed:
+                raise ValueError(f"{self!r} is closed")
+            self._users += 1
+
+    def _release(self):
+        with self._lock:
+            self._users -= 1
+            last = self.closed and self._users == 0
+        if last:
+            self._h = None
+            self._fin()
+
+    @property
+    def layout(self):
+        """imd_pack_layout of the spec: regions and sizes of the packed buffer (a dict)."""
+        if self._layout is None:
+            self._layout = host.pack_layout(self.spec, lib=self.lib.host)
+        return self._layout
+
+    @property
+    def record(self):
+        if self._rec is None:
+            self._rec = PackRecord(int(self.spec.N), self.spec.rounding, self.pack_bytes,
+                                   self.layout["key_digest"])
+        return self._rec
+
+    def pack(self, X, out, *, workspace=None, stream=None):
+        """imd_pack: X (float64, the spec's layout) -> `out` (>= pack_bytes, 256-byte aligned) on
+        `stream`; `workspace` >= workspace_bytes. A PackedBuffer `out` records this pack.
+        Returns out."""
+        if self.closed:
+            raise ValueError(f"{self!r} is closed")
+        s = 0 if stream is None else stream_handle(stream)
+        dev = self.handle.device
+        px = _pointer(X, self._x, s, device=dev)
+        pw, nw = _arrays.buffer(workspace, "workspace", stream=s, device=dev)
+        if isinstance(out, PackedBuffer):
+            po, no = out._resolve("packed buffer", True, s, dev)
+            with out._lock:   # the record follows host enqueue order
+                st = self._fn(self._h, px, po, no, pw, nw, s)
+                if st == 0:
+                    out._last = self.record
+                elif st == 6:  # the launches may have run in part
+                    out._last = None
+        else:
+            po, no = _arrays.buffer(out, "packed buffer", stream=s, device=dev)
+            st = self._fn(self._h, px, po, no, pw, nw, s)
+        if st:
+            raise _error(st, "imd_pack", f" (pack {self.pack_bytes} bytes, workspace "
+                                         f"{self.workspace_bytes} bytes needed; given {no}, {nw})")
+        return out
+
+    def pack_ptr(self, X, packed, packed_bytes, ws, ws_bytes, stream=0):
+        """imd_pack with raw integers: only the C checks, no PackedBuffer record."""
+        if self.closed:
+            raise ValueError(f"{self!r} is closed")
+        st = self._fn(self._h, X, packed, packed_bytes, ws, ws_bytes, stream)
+        if st:
+            raise _error(st, "imd_pack")
+
+    def close(self):
+        """Closed for new use at once; imd_pack_destroy runs when the last plan made with it is
+        closed or collected (those plans pass its handle at every call)."""
+        with self._lock:
+            self.closed = True
+            last = self._users == 0
+        if last:
+            self._h = None
+            self._fin()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __repr__(self):
+        return (f"<immerdink_b200.Pack {self.pack_bytes} bytes, workspace {self.workspace_bytes}"
+                f"{', closed' if self.closed else ''}>")
+
+
+class PackedBuffer:
+    """A caller-owned packed buffer that remembers the pack last written into it by Pack.pack
+    (recorded on the host at enqueue). A plan refuses one whose record differs from its slot's
+    pack, and one with no record. A safety net for the plain stream-ordered pattern only: the
+    record follows host order, not GPU order. buf: a contiguous CUDA array, an (int pointer,
+    nbytes) tuple, or an int pointer with `nbytes`. (ref: python/immerdink/device.py:422-495)"""
+
+    __slots__ = ("buf", "nbytes", "_last", "_lock")
+
+    def __init__(self, buf, nbytes=None):
+        if isinstance(buf, PackedBuffer):
+            raise TypeError("buf is already a PackedBuffer")
+        if buf is None:
+            raise ValueError("PackedBuffer needs a buffer")
+        if isinstance(buf, int):
+            if nbytes is None:
+                raise ValueError("a raw pointer needs nbytes")
+            buf = (buf, int(nbytes))
+        self.buf = buf
+        self.nbytes = None if nbytes is None else int(nbytes)
+        self._last = None
+        self._lock = threading.Lock()
+
+    @property
+    def last_pack(self):
+        return self._last
+
+    def _resolve(self, what, writable, stream, device):
+        p, n = _arrays.buffer(self.buf, what, writable, stream, device)
+        if self.nbytes is not None:
+            if self.nbytes > n:
+                raise ValueError(f"{what}: nbytes {self.nbytes} > the buffer's {n} bytes")
+            n = self.nbytes
+        return p, n
+
+    def _expect(self, rec, what):
+        with self._lock:
+            got = self._last
+        if got == rec:
+            return
+        if got is None:
+            msg = "no pack recorded (written only by Pack.pack into this PackedBuffer)"
+        elif got.N != rec.N:
+            msg = f"buffer last packed at N={got.N}, plan expects N={rec.N}"
+        elif got.rounding != rec.rounding:
+            msg = f"buffer last packed with {got.rounding}, plan expects {rec.rounding}"
+        else:
+            msg = (f"buffer last packed with another key (digest {got.key_digest:#x}, "
+                   f"{got.pack_bytes} bytes), plan expects digest {rec.key_digest:#x}")
+        raise PackMismatchError(f"{what}: {msg}")
+
+    def __repr__(self):
+        r = self._last
+        return ("<immerdink_b200.PackedBuffer " +
+                ("never packed" if r is None else
+                 f"last packed at N={r.N} {r.rounding}, {r.pack_bytes} bytes") + ">")
+
+
+def _pack_specs(packs):
+    """(PackSpec or None, PackSpec or None) of packs given as Pack / PackSpec / None."""
+    if packs is None:
+        return None
+    if len(packs) != 2:
+        raise ValueError("packs = (pack of A or None, pack of B or None)")
+    out = tuple(p.spec if isinstance(p, Pack) else p for p in packs)
+    return None if out == (None, None) else out
+
+
+def _finalize_plan(destroy, h, packs):
+    destroy(h)
+    for pk in packs:
+        pk._release()
+
+
 class Plan:
     """imd_plan_create for fixed operand layouts (arrays or `Layout`s). Immutable; any number
     of threads may call `contract` at once, each with its own workspace. Footprints:
@@ -182,9 +383,12 @@ class Plan:
         return self
 
     def _create(self, descs, N, g, rounding, mode, vec_mode, k4_tune, packs, handle, lib):
-        if packs is not None and any(p is not None for p in packs):
-            raise NotSupportedError("packed operands are not available in this build")
+        self._h = None
         self.lib = load_library(lib if handle is None else handle.lib)
+        self.packs = (None, None) if packs is None else tuple(packs)
+        if len(self.packs) != 2 or any(p is not None and not isinstance(p, Pack) for p in self.packs):
+            raise TypeError("packs = (Pack or None, Pack or None)")
+        self._packed = self.packs != (None, None)
         self.handle = handle or default_handle(self.lib)
         self.device = self.handle.device
         self.descs = descs
@@ -194,29 +398,59 @@ class Plan:
         self._cd = [host.CDesc(d) for d in descs]
         h = ct.c_void_p()
         L = self.lib.lib
-        st = L.imd_plan_create(self.handle._h, self._cd[0].t, self._cd[1].t, self._cd[2].t,
-                               self._opt, ct.byref(h))
-        if st:
-            raise _error(st, "imd_plan_create")
+        held = []
+        try:
+            for pk in self.packs:
+                if pk is not None:
+                    pk._acquire()
+                    held.append(pk)
+            if self._packed:
+                hp = [None if p is None else p._h for p in self.packs]
+                st = L.imd_plan_create_packed(self.handle._h, self._cd[0].t, self._cd[1].t,
+                                              self._cd[2].t, self._opt, hp[0], hp[1], ct.byref(h))
+            else:
+                st = L.imd_plan_create(self.handle._h, self._cd[0].t, self._cd[1].t, self._cd[2].t,
+                                       self._opt, ct.byref(h))
+            if st:
+                e = _error(st, "imd_plan_create" + ("_packed" if self._packed else ""))
+                if st == 8:
+                    e.reason = host.PACK_MISMATCH[self._lowering(check=False)["pack_mismatch"]]
+                    e.args = (e.args[0] + f" ({e.reason})",)
+                raise e
+        except BaseException:
+            for pk in held:
+                pk._release()
+            raise
         self._h = h.value
-        self._fin = weakref.finalize(self, L.imd_plan_destroy, h.value)
+        self._fin = weakref.finalize(self, _finalize_plan, L.imd_plan_destroy, h.value, tuple(held))
         self.workspace_bytes = host.workspace_size(descs, N=N, g=g, rounding=rounding, mode=mode,
-                                                   vec_mode=vec_mode, lib=self.lib.host)
+                                                   vec_mode=vec_mode, packing=_pack_specs(self.packs),
+                                                   lib=self.lib.host)
         nb = ct.c_size_t(0)
         L.imd_plan_device_bytes(self._h, ct.byref(nb))
         self.device_bytes = nb.value
         self._ex = [_Expected(d, n) for d, n in zip(descs, "ABC")]
-        self._fn = L.imd_contract
+        self._fn = L.imd_contract_packed if self._packed else L.imd_contract
         self._lw = None
+
+    def _lowering(self, sm_count=0, check=True):
+        o = self.options
+        return host.lowering(self.descs, N=o["N"], g=o["g"], rounding=o["rounding"],
+                             mode=o["mode"], vec_mode=o["vec_mode"], sm_count=sm_count,
+                             packing=_pack_specs(self.packs), lib=self.lib.host, check=check)
 
     @property
     def lowering(self):
         if self._lw is None:
-            o = self.options
-            self._lw = host.lowering(self.descs, N=o["N"], g=o["g"], rounding=o["rounding"],
-                                     mode=o["mode"], vec_mode=o["vec_mode"],
-                                     sm_count=self.lib.sm_count(self.device), lib=self.lib.host)
+            self._lw = self._lowering(self.lib.sm_count(self.device))
         return self._lw
+
+    def pack_spec(self, operand):
+        """imd_pack_desc_for of operand 0 (A) or 1 (B) for this plan's descriptors and options."""
+        o = self.options
+        return host.pack_desc_for(self.descs, operand=operand, N=o["N"], g=o["g"],
+                                  rounding=o["rounding"], mode=o["mode"], vec_mode=o["vec_mode"],
+                                  lib=self.lib.host)
 
     @property
     def host_bytes(self):
@@ -228,8 +462,6 @@ class Plan:
         Returns C."""
         if self._h is None:
             raise ValueError("plan is closed")
-        if packed is not None and any(x is not None for x in packed):
-            raise ValueError("packed buffers given to a plan without packs")
         s = 0 if stream is None else stream_handle(stream)
         dev = self.device
         pa = _pointer(A, self._ex[0], s, device=dev)
@@ -237,14 +469,45 @@ class Plan:
         pc = _pointer(C, self._ex[2], s, True, dev)
         pw, nw = (None, 0) if workspace is None else _arrays.buffer(workspace, "workspace",
                                                                     stream=s, device=dev)
-        st = self._fn(self._h, alpha, pa, pb, beta, pc, pw, nw, s)
+        if self._packed:
+            st = self._fn(self._h, alpha, *self._operands(pa, pb, packed, s), beta, pc, pw, nw, s)
+        else:
+            if packed is not None and any(x is not None for x in packed):
+                raise ValueError("packed buffers given to a plan without packs")
+            st = self._fn(self._h, alpha, pa, pb, beta, pc, pw, nw, s)
         if st:
             raise self._fail(st, nw)
         return C
 
-    def contract_ptr(self, alpha, A, B, beta, C, ws, ws_bytes, stream=0):
-        """imd_contract with raw integers: only the C checks."""
-        st = self._fn(self._h, alpha, A, B, beta, C, ws, ws_bytes, stream)
+    def _operands(self, pa, pb, packed, s):
+        packed = (None, None) if packed is None else packed
+        if len(packed) != 2:
+            raise ValueError("packed = (buffer or None, buffer or None)")
+        ops = []
+        for x, (data, buf, pk) in enumerate(zip((pa, pb), packed, self.packs)):
+            if pk is None:
+                if buf is not None:
+                    raise ValueError(f"packed[{x}] given for an in-line operand")
+                ops.append(_capi.Operand(data, None, 0, None))
+                continue
+            if isinstance(buf, PackedBuffer):
+                buf._expect(pk.record, f"packed[{x}]")
+                p, n = buf._resolve(f"packed[{x}]", False, s, self.device)
+            elif isinstance(buf, tuple) or buf is None:
+                p, n = _arrays.buffer(buf, f"packed[{x}]")
+            else:
+                p, n = _arrays.buffer(buf, f"packed[{x}]", False, s, self.device)
+            ops.append(_capi.Operand(data, p, n, pk._h))
+        return ct.byref(ops[0]), ct.byref(ops[1])
+
+    def contract_ptr(self, alpha, A, B, beta, C, ws, ws_bytes, stream=0, packed=None):
+        """imd_contract with raw integers: only the C checks. packed = ((ptr, nbytes) or None,
+        ...) for a packed plan."""
+        if self._packed:
+            st = self._fn(self._h, alpha, *self._operands(A, B, packed, stream), beta, C, ws,
+                          ws_bytes, stream)
+        else:
+            st = self._fn(self._h, alpha, A, B, beta, C, ws, ws_bytes, stream)
         if st:
             raise self._fail(st, ws_bytes)
 
@@ -252,7 +515,7 @@ class Plan:
         extra = ""
         if st in (1, 4) and nw < self.workspace_bytes:
             extra = f" (workspace of {nw} bytes; the plan needs {self.workspace_bytes})"
-        return _error(st, "imd_contract", extra)
+        return _error(st, "imd_contract" + ("_packed" if self._packed else ""), extra)
 
     def close(self):
         self._h = None
@@ -307,7 +570,8 @@ class PlanCache:
         lib = load_library(lib)
         lays = tuple(_layout(x, n) for x, n in zip((A, B, C), "ABC"))
         opts = (int(N), int(g), rounding, mode, vec_mode, bool(k4_tune))
-        key = (spec, lays, opts, id(lib), lib.current_device())
+        pk = None if packs is None else tuple(None if p is None else id(p) for p in packs)
+        key = (spec, lays, opts, pk, id(lib), lib.current_device())
         return self._get(key, lambda: Plan(spec, *lays, N=N, g=g, rounding=rounding, mode=mode,
                                            vec_mode=vec_mode, k4_tune=k4_tune, packs=packs, lib=lib))
 
@@ -347,4 +611,5 @@ def workspace_size(spec, A, B, C, *, N, g=0, rounding="RN", mode="EMULATE", vec_
                    packs=None, lib=None):
     """Exact workspace bytes for these operands (arrays or `Layout`s); host library only."""
     descs = _descs(spec, [_layout(x, n) for x, n in zip((A, B, C), "ABC")])
-    return host.workspace_size(descs, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode)
+    return host.workspace_size(descs, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode,
+                               packing=_pack_specs(packs), lib=load_library(lib).host)

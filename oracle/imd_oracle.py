@@ -191,8 +191,9 @@ def _radix(modes, X):
     return v
 
 
-def lower(A, B, C, mode="EMULATE"):
-    """The lowering with legality rows 1-5 in precedence order."""
+def lower(A, B, C, mode="EMULATE", orders=None):
+    """The lowering with legality rows 1-5 in precedence order. `orders` ({post-swap class:
+    [labels]}): canonical orders adopted from packed operands (spec/oracle.py:831-836)."""
     T = {"A": A, "B": B, "C": C}
     for d in T.values():
         if any(e < 0 for e in d.extent):
@@ -257,6 +258,10 @@ def lower(A, B, C, mode="EMULATE"):
             "K": lambda l: (a(big, l), a(oth, l), first[l])}
     v.order = {g: sorted((l for l in cls if cls[l] == g and ext[l] != 1), key=keys[g])
                for g in "IJKL"}
+    for g, lst in (orders or {}).items():
+        assert sorted(lst) == sorted(v.order[g]), "an adopted order permutes the class's labels"
+        v.order[g] = list(lst)
+    v.ext, v.stride = ext, stride
     v.fused = {}
     for g in "IJKL":
         fused = []
@@ -284,7 +289,8 @@ def vec(view, name):
 
 # ----------------------------------------------------------------------------- tensor level
 def contract_tensor(A, B, Cbuf, dA, dB, dC, alpha, beta, N, rounding="RN", mode="EMULATE",
-                    baseA=0, baseB=0, baseC=0, literal=False, chunk=0, rows=None, cols=None):
+                    baseA=0, baseB=0, baseC=0, literal=False, chunk=0, rows=None, cols=None,
+                    orders=None):
     """C <- alpha A B + beta C on flat float64 buffers with descriptors (extent, element stride,
     label); base* is the buffer index of the all-zero multi-index. Returns a new flat C buffer.
 
@@ -293,7 +299,7 @@ def contract_tensor(A, B, Cbuf, dA, dB, dC, alpha, beta, N, rounding="RN", mode=
     InvalidValue / NotSupported."""
     if not (2 <= N <= 20) or rounding not in ("RN", "TRUNC") or mode not in ("EMULATE", "DIRECT"):
         raise InvalidValue("option")
-    view = lower(dA, dB, dC, mode)
+    view = lower(dA, dB, dC, mode, orders)
     out = np.array(Cbuf, dtype=np.float64, copy=True)
     if view.empty_output:
         return out
@@ -330,6 +336,122 @@ def contract_tensor(A, B, Cbuf, dA, dB, dC, alpha, beta, N, rounding="RN", mode=
             else:
                 res = gemm(Al, Bl, N, alpha, beta, Cl, rounding, literal, chunk)
         out[cidx] = res
+    return out
+
+
+# ----------------------------------------------------------------------------- packed operands
+K_PAD64_MIN = 96   # k > 96: K rows padded to 64 (pack format 2), else to 16 (format 1)
+
+
+class PackView:
+    pass
+
+
+def pack_view(X, contracted, batch, rows=None, order="AUTO", N=14, rounding="RN"):
+    """Lowering of one operand X for packing (spec/oracle.py:1122-1186): classes K (contracted),
+    L (batch), R (rows: listed for GIVEN, the rest of X's labels for AUTO); extent-1 labels
+    dropped; AUTO orders a class by (|merged stride|, first position); modes fused over X's
+    strides alone; byte layout of spec/oracle.py:1085-1102."""
+    if not (2 <= N <= 20) or rounding not in ("RN", "TRUNC") or order not in ("AUTO", "GIVEN"):
+        raise InvalidValue("option")
+    if any(e < 0 for e in X.extent):
+        raise InvalidValue("negative extent")
+    ext, ms, first = {}, {}, {}
+    for p, (e, st, l) in enumerate(zip(X.extent, X.stride, X.label)):
+        if ext.setdefault(l, e) != e:
+            raise InvalidValue("extent mismatch")
+        ms[l] = ms.get(l, 0) + st
+        first.setdefault(l, p)
+    K, L = list(contracted), list(batch)
+    if order == "AUTO":
+        if rows:
+            raise InvalidValue("AUTO with rows")
+        R = None
+    else:
+        R = list(rows or [])
+    listed = K + L + (R or [])
+    if any(l not in ext for l in listed) or len(set(listed)) != len(listed):
+        raise InvalidValue("labels")
+    if R is None:
+        R = [l for l in ext if l not in K and l not in L]
+    elif set(listed) != set(ext):
+        raise InvalidValue("GIVEN without every label")
+    if any(abs(v) > INT64_MAX for v in ms.values()):
+        raise InvalidValue("merged stride")
+    if not X.empty() and sum(abs(s) * (e - 1) for e, s in zip(X.extent, X.stride)) > INT64_MAX:
+        raise InvalidValue("span")
+    lists = {"K": K, "L": L, "R": R}
+    size = {c: math.prod(ext[l] for l in lists[c] if ext[l] != 1) for c in "KLR"}
+    if any(v > INT64_MAX for v in size.values()):
+        raise InvalidValue("extent product")
+    v = PackView()
+    v.N, v.rounding = N, rounding
+    v.b, v.r, v.k = size["L"], size["R"], size["K"]
+    v.format = 2 if v.k > K_PAD64_MIN else 1
+    align = 64 if v.format == 2 else 16
+    v.k_hat = -(-v.k // align) * align
+    v.regs, v.pack_bytes = {}, 0
+    if v.b * v.r * v.k != 0:
+        off = 0
+        for name, nbytes in (("sig", 2 * v.b * v.r), ("flag", v.b * v.r),
+                             ("res", N * v.b * v.r * v.k_hat + (-(-v.r // 16) * 16 - v.r) * v.k_hat)):
+            v.regs[name] = (off, nbytes)
+            off += -(-nbytes // 256) * 256
+            if off > 2**64 - 1:
+                raise InvalidValue("pack size")
+        v.pack_bytes = off
+    if not any(ext[l] != 1 for l in K):
+        raise NotSupported("K empty after lowering")
+    if rounding == "RN" and v.k >= 2:
+        kappa = math.isqrt(v.k)
+        kappa += kappa * kappa != v.k
+        if kappa >= constants(N)[2]:
+            raise NotSupported("kappa >= T")
+    key = (lambda l: (abs(ms[l]), first[l])) if order == "AUTO" else None
+    v.order = {c: [l for l in (sorted(lists[c], key=key) if key else lists[c]) if ext[l] != 1]
+               for c in "KLR"}
+    v.fused = {}
+    for c in "LRK":
+        fused = []
+        for l in v.order[c]:
+            if fused and ms[l] == fused[-1][1] * fused[-1][0]:
+                fused[-1][0] *= ext[l]
+            else:
+                fused.append([ext[l], ms[l]])
+        v.fused[c] = fused
+    words = [v.format, N, 0 if rounding == "RN" else 1, v.b, v.r, v.k]
+    for c in "LRK":
+        words.append(len(v.fused[c]))
+        for e, st in v.fused[c]:
+            words += [e, st]
+    v.key = tuple(words)
+    h = 0xcbf29ce484222325
+    for w in words:
+        for byte in (w & (2**64 - 1)).to_bytes(8, "little"):
+            h = ((h ^ byte) * 0x100000001b3) & (2**64 - 1)
+    v.digest = h
+    return v
+
+
+def pack(Xbuf, base, v):
+    """The packed bytes of X (spec/oracle.py:1193-1224): per row (batch, row) its shift and
+    flag, then the N residue planes over the canonical K with zero K padding, a zero tail and
+    zero alignment gaps."""
+    out = np.zeros(v.pack_bytes, np.uint8)
+    if v.pack_bytes == 0:
+        return out
+    vec_of = lambda c: _radix([(e, {"X": st}) for e, st in v.fused[c]], "X")
+    vL, vR, vK = vec_of("L"), vec_of("R"), vec_of("K")
+    rows = np.asarray(Xbuf, np.float64)[base + (vL[:, None] + vR[None, :]).reshape(-1)[:, None]
+                                        + vK[None, :]]
+    sig, fl = scale(rows, v.N, v.rounding)
+    R = residues(rows, sig, v.N, v.rounding)            # [N][b r][k]
+    so, fo, ro_ = v.regs["sig"][0], v.regs["flag"][0], v.regs["res"][0]
+    out[so:so + 2 * len(sig)] = sig.astype("<i2").view(np.uint8)
+    out[fo:fo + len(fl)] = fl
+    planes = np.zeros((v.N, v.b * v.r, v.k_hat), np.int8)
+    planes[:, :, :v.k] = R
+    out[ro_:ro_ + planes.size] = planes.reshape(-1).view(np.uint8)
     return out
 
 

@@ -3,7 +3,7 @@
 
 Run once where the reference tree is present:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py [/path/to/reference [file names to regenerate...]]
 
 The fixtures pin the CPU oracle in oracle/ (and through it the CUDA library): every array is
 stored as raw bit patterns, so the comparison is bit for bit. The input constructions below
@@ -16,6 +16,8 @@ Files written:
                oracle.contract_tensor, and the lowering summary of each (m, n, k, b, swapped,
                canonical orders, scatter vectors)
   status.npz   descriptor sets with the status the reference's lowering raises
+  pack.npz     packed operands: pack descriptors, layouts, keys and the packed BYTES from
+               oracle.pack, and oracle.contract_tensor(packs=...) outputs
 """
 import json
 import math
@@ -381,8 +383,121 @@ def run_status(out):
     print("status:", [(e["name"], e["status"]) for e in manifest])
 
 
+# --------------------------------------------------------------------------- packed operands
+def pack_cases():
+    cases = []
+
+    def add(name, spec, ext, **kw):
+        cases.append(dict(name=name, spec=spec, ext=ext, layouts=kw.get("layouts") or [None] * 3,
+                          N=kw.get("N", 14), rounding=kw.get("rounding", "RN"), gen=kw.get("gen"),
+                          alpha=kw.get("alpha", 1.0), beta=kw.get("beta", 0.0),
+                          pad=kw.get("pad") or [None] * 3, negate=kw.get("negate") or [None] * 3))
+
+    add("matrix", "ik,kj->ij", dict(i=5, j=6, k=11))
+    add("matrix_N7_trunc", "ik,kj->ij", dict(i=4, j=3, k=9), N=7, rounding="TRUNC")
+    add("matrix_N18", "ik,kj->ij", dict(i=3, j=4, k=7), N=18, alpha=1.5, beta=0.5)
+    add("k_over_96", "ik,kj->ij", dict(i=3, j=2, k=99), N=6)
+    add("swapped", "ik,kj->ji", dict(i=4, j=3, k=5))
+    add("three_mode", "ijk,kl->lij", dict(i=3, j=2, k=6, l=3))
+    add("two_k", "kjbc,kiac->abij", dict(a=2, b=2, c=3, i=2, j=2, k=2))
+    add("batch", "bik,bkj->bij", dict(b=3, i=2, j=4, k=5), beta=1.0)
+    add("batch_fast", "ikb,kjb->ijb", dict(b=2, i=3, j=4, k=5))
+    add("permuted", "kji,lk->jli", dict(i=3, j=2, k=4, l=3), layouts=[[1, 0, 2], [1, 0], [2, 0, 1]])
+    add("neg_padded", "ik,kj->ij", dict(i=4, j=3, k=5), negate=[[1], [0, 1], None],
+        pad=[{1: 2}, None, None])
+    add("specials", "ik,kj->ij", dict(i=4, j=4, k=6), gen="specials", alpha=2.0, beta=0.5)
+    add("extent1", "iak,kbj->iabj", dict(i=3, a=1, k=4, b=1, j=2))
+    add("diag", "iik,kj->ij", dict(i=3, j=4, k=5))
+    add("k_orders_differ", "kci,ckj->ij", dict(i=3, j=2, k=3, c=4))
+    add("k_extent1", "ik,kj->ij", dict(i=3, j=4, k=1))
+    return cases
+
+
+def run_pack(out):
+    """Packed operands: for each case and caller operand, the AUTO and the GIVEN pack (its
+    descriptor, layout, key and BYTES), and the contraction through packs of A, of B and of both."""
+    rng = random.Random(4242)
+    gens = dict(uniform=gen_uniform(rng))
+    special_vals = [math.inf, -math.inf, math.nan, 0.0, -0.0, 1e308, -1e308]
+    gens["specials"] = lambda: (rng.choice(special_vals) if rng.random() < 0.08
+                                else rng.uniform(-1, 1))
+    manifest = []
+    for ci, c in enumerate(pack_cases()):
+        ins, outl = c["spec"].split("->")
+        la, lb = ins.split(",")
+        gen = gens[c["gen"] or "uniform"]
+        tens = [build_tensor(rng, lab, c["ext"], c["layouts"][x], c["pad"][x], c["negate"][x], gen)
+                for x, lab in enumerate((la, lb, outl))]
+        key = f"p{ci}"
+        entry = dict(name=c["name"], key=key, spec=c["spec"], N=c["N"], rounding=c["rounding"],
+                     alpha=bits(c["alpha"]), beta=bits(c["beta"]),
+                     desc=[dict(extent=t.desc.extent, stride=t.desc.stride, label=t.desc.label,
+                                base=t.base) for t in tens], packs=[], runs=[])
+        for x, t in zip("ABC", tens):
+            out[f"{key}_{x}"] = np.array([bits(v) for v in t.buf], np.uint64)
+        made = {}
+        for x, (lab, other) in enumerate(((la, lb), (lb, la))):
+            for order in ("AUTO", "GIVEN"):
+                if order == "AUTO":
+                    kl = [ord(l) for l in dict.fromkeys(lab) if l not in outl]
+                    bl = [ord(l) for l in dict.fromkeys(lab) if l in outl and l in other]
+                    pd = ro.PackDesc(tens[x].desc, c["N"], c["rounding"], "AUTO", kl, bl, None)
+                else:
+                    pd = ro.pack_desc_for(tens[0].desc, tens[1].desc, tens[2].desc, "EMULATE", x,
+                                          c["N"], c["rounding"])
+                rec = dict(operand=x, order=order, contracted=pd.contracted, batch=pd.batch,
+                           rows=pd.rows or [])
+                try:
+                    tr = {}
+                    data = ro.pack(tens[x], pd, tr)
+                    v = tr.get("view") or ro.pack_lower(pd)
+                    tag = f"{key}_pack{x}{order[0]}"
+                    out[tag] = np.frombuffer(bytes(data), np.uint8)
+                    rec.update(status="SUCCESS", tag=tag, b=v.b, r=v.r, k=v.k, k_hat=v.k_hat,
+                               format=v.format, pack_bytes=v.pack_bytes, key=list(v.key),
+                               digest=v.digest, order_K=v.order["K"], order_L=v.order["L"],
+                               order_R=v.order["R"],
+                               regs={n: list(v.regs[n]) for n in v.regs})
+                    made[(x, order)] = ro.PackedOperand(pd, data)
+                except ro.NotSupported:
+                    rec["status"] = "NOT_SUPPORTED"
+                except ro.InvalidValue:
+                    rec["status"] = "INVALID_VALUE"
+                entry["packs"].append(rec)
+        for order in ("AUTO", "GIVEN"):
+            for which in ((0,), (1,), (0, 1)):
+                if any((x, order) not in made for x in which):
+                    continue
+                packs = tuple(made[(x, order)] if x in which else None for x in (0, 1))
+                run = dict(order=order, which=list(which))
+                try:
+                    tr = {}
+                    res = ro.contract_tensor(tens[0], tens[1], tens[2], c["alpha"], c["beta"],
+                                             c["N"], c["rounding"], None, "EMULATE", trace=tr,
+                                             packs=packs)
+                    tag = f"{key}_out{order[0]}{''.join(map(str, which))}"
+                    out[tag] = np.array([bits(v) for v in res], np.uint64)
+                    run.update(status="SUCCESS", tag=tag, kind=tr["kind"],
+                               orders={g: lst for g, lst in tr["packed"]["orders"].items()})
+                except ro.PackMismatch as e:
+                    run.update(status="PACK_MISMATCH", reason=e.reason)
+                except ro.NotSupported:
+                    run["status"] = "NOT_SUPPORTED"
+                entry["runs"].append(run)
+        manifest.append(entry)
+    out["manifest"] = np.frombuffer(json.dumps(manifest).encode(), np.uint8)
+    print("pack:", len(manifest), "cases;",
+          sum(len(e["packs"]) for e in manifest), "packs;",
+          {s: sum(1 for e in manifest for r in e["runs"] if r["status"] == s)
+           for s in ("SUCCESS", "PACK_MISMATCH", "NOT_SUPPORTED")})
+
+
 if __name__ == "__main__":
-    for name, fn in (("matrix", run_matrix), ("tensor", run_tensor), ("status", run_status)):
+    only = sys.argv[2:]   # e.g. "pack": regenerate that file alone
+    for name, fn in (("matrix", run_matrix), ("tensor", run_tensor), ("status", run_status),
+                     ("pack", run_pack)):
+        if only and name not in only:
+            continue
         data = {}
         fn(data)
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
