@@ -6,6 +6,8 @@
   float64 CUDA arrays (`__cuda_array_interface__`, DLPack, raw pointers) over the C ABI of
   libimmerdink.so. Importing loads no library; libimmerdink.so is loaded on first use and the
   call fails loudly when it is missing (there is no CPU fallback).
+- `immerdink_b200.hostpipe.HostContraction`: operands in pinned host memory, copies overlapped
+  with the contraction slab by slab (imported on demand: needs torch and cuda-python).
 """
 from .device import (AliasingError, AllocFailedError, CudaError, DeviceArray, Handle,  # noqa: F401
                      ImmerdinkError, InsufficientWorkspaceError, InvalidValueError, Layout,
