@@ -325,6 +325,10 @@ IMD_API double imd_prof_mma_peak(int pair) {
     return 0.0;
   return imd::mma_probe_tops(pair, sms);
 }
+IMD_API int imd_test_gemm_band_mb(int mb) {
+  if (mb > 0) imd::gemm_band_mb() = mb;
+  return imd::gemm_band_mb();
+}
 IMD_API int imd_test_gemm_variant(int v) {
   imd::gemm_variant() = v;
   return 0;

@@ -130,12 +130,15 @@ struct GemmParams {
   GemmShape s;
   int32_t tiles_m, tiles_n;
   int32_t k_blocks;
+  int32_t band_rows;  // tile rows walked together (see tile_of)
   uint8_t* W;
   unsigned int* error_word;
 };
 
-// Work item -> (plane, tile row, tile column). Tile rows are walked in bands of 16 so that the
-// CTAs running at the same time share A rows and B rows in L2.
+// Work item -> (plane, tile row, tile column). Tile rows are walked in bands of `band_rows`, tile
+// row fastest: the band's rows of A stay in L2 while the rows of B stream through once per band,
+// so DRAM reads A once and B (tile rows / band_rows) times per plane. The host sizes the band to
+// about a quarter of L2.
 struct TileCoord {
   int plane, tm, tn;
 };
@@ -144,9 +147,9 @@ __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int64_t w) {
   TileCoord c;
   c.plane = static_cast<int>(w / per_plane);
   const int t = static_cast<int>(w % per_plane);
-  const int band = 16 * p.tiles_n;
-  const int first = (t / band) * 16;
-  const int rows = min(p.tiles_m - first, 16);
+  const int band = p.band_rows * p.tiles_n;
+  const int first = (t / band) * p.band_rows;
+  const int rows = min(p.tiles_m - first, p.band_rows);
   const int r = t % band;
   c.tm = first + r % rows;
   c.tn = r / rows;
@@ -427,15 +430,15 @@ __device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc,
       : "memory");
 }
 
-// Work item -> (plane, 256-row tile, 256-column tile), bands of 8 tile rows.
+// Work item -> (plane, 256-row tile, 256-column tile), bands as in tile_of.
 __device__ __forceinline__ TileCoord pair_tile_of(const GemmParams& p, int64_t w) {
   const int per_plane = p.tiles_m * p.tiles_n;
   TileCoord c;
   c.plane = static_cast<int>(w / per_plane);
   const int t = static_cast<int>(w % per_plane);
-  const int band = 8 * p.tiles_n;
-  const int first = (t / band) * 8;
-  const int rows = min(p.tiles_m - first, 8);
+  const int band = p.band_rows * p.tiles_n;
+  const int first = (t / band) * p.band_rows;
+  const int rows = min(p.tiles_m - first, p.band_rows);
   const int r = t % band;
   c.tm = first + r % rows;
   c.tn = r / rows;
@@ -718,6 +721,15 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
   p.tiles_m = (s.m + (pair ? 256 : kTileM) - 1) / (pair ? 256 : kTileM);
   p.tiles_n = (s.n_hat + kTileN - 1) / kTileN;
   p.k_blocks = (s.klen + kTileK - 1) / kTileK;
+  {
+    // rows of A that stay resident: about 32 MB of the 126 MB L2 (the B rows in flight, the
+    // product tiles being written and the other die's copies share the rest)
+    const int64_t tile_bytes = static_cast<int64_t>(pair ? 256 : kTileM) * (s.klen > 0 ? s.klen : 1);
+    int64_t rows = (static_cast<int64_t>(gemm_band_mb()) << 20) / tile_bytes;
+    rows = rows < 4 ? 4 : rows;
+    p.band_rows = static_cast<int32_t>(rows < p.tiles_m ? rows : p.tiles_m);
+    if (p.band_rows < 1) p.band_rows = 1;
+  }
   p.W = W;
   p.error_word = info.error_word;
   const int64_t total = static_cast<int64_t>(s.planes) * p.tiles_m * p.tiles_n;
@@ -754,6 +766,11 @@ double mma_probe_tops(int pair, int sms) {
   const double issuers = pair ? grid / 2 : grid;
   const double ops = 2.0 * (pair ? 256.0 : 128.0) * 256.0 * 32.0 * iters * issuers;
   return ops / (ms * 1e-3);
+}
+
+int& gemm_band_mb() {
+  static int v = 32;  // tuning hook: MB of A rows kept L2-resident by the tile order
+  return v;
 }
 
 int& gemm_variant() {

@@ -60,6 +60,8 @@ bool& use_reference_gemm();
 // Verification switch for the tensor-core kernel: 0 = chosen by shape, 1 = one CTA per 128 x 256
 // tile, 2 = CTA pairs on 256 x 256 tiles.
 int& gemm_variant();
+// Tuning hook: MB of operand A's tile rows that the tile order keeps resident in L2 (default 32).
+int& gemm_band_mb();
 // Benchmark hook: int8 ops per second of back-to-back tcgen05.mma.kind::i8 with no loads.
 double mma_probe_tops(int pair, int sms);
 
