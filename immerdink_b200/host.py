@@ -9,9 +9,10 @@ estimates, straight from libimmerdink_host.so (ctypes). Nothing is recomputed in
     host.err_estimate(N=14, k=8000)
 
 Mirrors the reference's python/immerdink/host.py for the queries of the contraction path
-(workspace_size :?, lowering, workspace_layout, plan_bytes, g_tradeoff, err_estimate, min_moduli):
-same names, arguments (einsum spec + extents dict, or raw (extent, stride, label) descriptors)
-and error type. The performance-model and packed-operand queries are not provided yet.
+(workspace_size, lowering, workspace_layout, plan_bytes, g_tradeoff, err_estimate, min_moduli) and
+of packed operands (PackSpec, pack_layout, pack_desc_for, `packing=` of workspace_size and
+lowering): same names, arguments (einsum spec + extents dict, or raw (extent, stride, label)
+descriptors) and error type. The performance-model queries are not provided.
 
 Library search: `lib=` path, $IMMERDINK_HOST_LIB, $IMMERDINK_LIB_DIR/libimmerdink_host.so, the
 package directory.
