@@ -19,8 +19,10 @@ moduli, residue group 7, alpha = 1, beta = 0, seeded synthetic uniform [-1, 1) o
 With N > 1 ranks (torchrun) the output C is partitioned over its free modes a and b
 (immerdink_b200.dist): every rank owns 1/N of A and of B, all-gathers the slabs of its tile over
 NCCL inside its grid column / row, and computes the tile with its own plan; no collective follows.
-`value` times the contraction with the slabs gathered (strong scaling of the one contraction);
-the all-gather is timed separately (`exchange_ms`, `value_with_exchange`).
+A timed step is the WHOLE exchange + contraction of every rank (immerdink_b200.dist.RankContraction:
+the all-gathers run on a side stream, A is packed while B's slab arrives); `value` is strong scaling
+of the one contraction, max over ranks. `config` also gives the all-gathers alone and the
+contraction with the slabs already gathered.
 """
 import argparse
 import json
@@ -244,7 +246,7 @@ def run_ours(args, rank, world, local_rank):
         off = slab_offsets_torch(shape, prob.shape(x, False), [start.get(c, 0) for c in labels], dev)
         return mix_torch(off, prob.seeds[x]).contiguous()
 
-    exchange = None
+    exchange = rankc = None
     if world == 1:
         A = synth(0, prob.shape(0), {})
         B = synth(1, prob.shape(1), {})
@@ -252,18 +254,16 @@ def run_ours(args, rank, world, local_rank):
         plan = imd.Plan(prob.spec, A, B, Cd, N=prob.N, g=prob.g)
         run_spec = prob.spec
     else:
+        # every rank owns 1/world of A and of B; a step = exchange of the slabs + the rank's tile
         shard_a = synth(0, part.shard_shape(0), part.shard_start(0))
         shard_b = synth(1, part.shard_shape(1), part.shard_start(1))
-        A = torch.empty(part.gathered_shape(0), dtype=torch.float64, device=dev)
-        B = torch.empty(part.gathered_shape(1), dtype=torch.float64, device=dev)
         groups = idist.make_groups(world, dist)
+        rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups)
+        A, B, plan, run_spec = rankc.A, rankc.B, rankc.plan, rankc.spec
+        Cd = torch.empty(rankc.tile_shape, dtype=torch.float64, device=dev)
 
         def exchange():
             idist.gather(part, shard_a, shard_b, A, B, groups, dist)
-        exchange()
-        run_spec, _, _, lc = part.plan_layouts()
-        Cd = torch.empty(lc.shape, dtype=torch.float64, device=dev)
-        plan = imd.Plan(run_spec, A, B, Cd, N=prob.N, g=prob.g)
     ws = torch.empty(plan.workspace_bytes + 256, dtype=torch.uint8, device=dev)
     off = (-ws.data_ptr()) % 256
     wsv = ws[off:off + plan.workspace_bytes]
@@ -272,7 +272,10 @@ def run_ours(args, rank, world, local_rank):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
 
     def step():
-        plan.contract(A, B, Cd, workspace=wsv, stream=stream)
+        if rankc is None:
+            plan.contract(A, B, Cd, workspace=wsv, stream=stream)
+        else:
+            rankc(shard_a, shard_b, Cd)
 
     def barrier():
         if world > 1:
@@ -302,7 +305,7 @@ def run_ours(args, rank, world, local_rank):
     lib.lib.imd_prof_read(phases, 8)
     lib.lib.imd_prof_enable(0)
     phase_ms = {name: phases[t] / args.steps for t, name in
-                ((1, "vectors+scale"), (2, "residues"), (3, "gemm"), (4, "crt"))}
+                ((1, "vectors+scale"), (2, "residues"), (3, "gemm"), (4, "crt"), (6, "pack"))}
     t_ms = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
@@ -321,9 +324,10 @@ def run_ours(args, rank, world, local_rank):
     def e2e_step():
         dA2.copy_(hA, non_blocking=True)
         dB2.copy_(hB, non_blocking=True)
-        if exchange is not None:
-            exchange()
-        imd.contract(run_spec, inA, inB, Cd, N=prob.N, g=prob.g, workspace=wsv, stream=stream)
+        if rankc is None:
+            imd.contract(run_spec, inA, inB, Cd, N=prob.N, g=prob.g, workspace=wsv, stream=stream)
+        else:
+            rankc(dA2, dB2, Cd)
         hC.copy_(Cd, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 5))
@@ -340,7 +344,9 @@ def run_ours(args, rank, world, local_rank):
         return e0.elapsed_time(e1) / e2e_steps
 
     serial_ms = time_e2e(e2e_step)     # copy in, one call, copy out: one after the other
-    e2e_ms, e2e_how, e2e_exact = serial_ms, "H2D A, B; one imd_contract; D2H C (in sequence)", None
+    e2e_ms, e2e_exact = serial_ms, None
+    e2e_how = ("H2D A, B; one imd_contract; D2H C (in sequence)" if world == 1 else
+               "per rank: H2D of its pieces of A and B; exchange + contraction (dist.RankContraction); D2H of its C tile")
     if world == 1:
         # the same host operands through the slab pipeline of the package: copies overlap the
         # contraction, the shared operand is packed once
@@ -360,19 +366,25 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_ms = float(t_e2e.item())
-    exchange_ms = 0.0
+    exchange_ms = resident_ms = 0.0
     if exchange is not None:
-        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        exchange()
-        barrier()
-        x0.record(stream)
-        for _ in range(5):
-            exchange()
-        x1.record(stream)
-        barrier()
-        t_x = torch.tensor([x0.elapsed_time(x1) / 5], dtype=torch.float64, device=dev)
-        dist.all_reduce(t_x, op=dist.ReduceOp.MAX)
-        exchange_ms = float(t_x.item())
+        def timed(fn, reps=5):
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            fn()
+            barrier()
+            x0.record(stream)
+            for _ in range(reps):
+                fn()
+            x1.record(stream)
+            barrier()
+            t = torch.tensor([x0.elapsed_time(x1) / reps], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        exchange_ms = timed(exchange)            # the two all-gathers alone
+        plain = imd.Plan(run_spec, A, B, Cd, N=prob.N, g=prob.g)
+        wsp = torch.empty(plain.workspace_bytes, dtype=torch.uint8, device=dev)
+        resident_ms = timed(lambda: plain.contract(A, B, Cd, workspace=wsp, stream=stream))
+        plain.close()
     err = lib.lib.imd_test_device_error()
 
     if rank != 0:
@@ -400,17 +412,18 @@ def run_ours(args, rank, world, local_rank):
                 dtype="int8xint8->int32 (FP64 emulation)", data="synthetic",
                 config=dict(workload=f"{args.workload}: {prob.spec} {prob.ext} N={prob.N} g={prob.g} "
                                      "alpha=1 beta=0, uniform[-1,1)",
-                            partition=f"C modes (a,b) over {GRID[world]} ranks; slabs all-gathered over "
-                                      "NCCL before the timed contraction",
-                            exchange_ms=exchange_ms,
-                            value_with_exchange=flops / ((ms_max + exchange_ms) * 1e-3) / 1e12,
+                            partition=(f"C modes (a,b) over {GRID[world]} ranks" + ("" if world == 1 else
+                                       "; every step all-gathers the slabs over NCCL (side stream), packs A "
+                                       "while B arrives and contracts the rank's tile")),
+                            exchange_alone_ms=exchange_ms, contraction_slabs_resident_ms=resident_ms,
                             l2="256 MB buffer written between timed steps",
                             gemm_view=[low["m"], low["n"], low["k"], low["b"]]),
                 e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOPS-eq",
                          h2d_bytes_per_step=(srcA.numel() + srcB.numel()) * 8 * world,
                          d2h_bytes_per_step=Cd.numel() * 8 * world, ms_per_step=e2e_ms,
                          how=e2e_how, serial_ms=serial_ms, equals_device_result=e2e_exact),
-                gpu_launches=int(low["kernel_launches"]) * args.steps * world,
+                # per step: the plan's launches (+ the 4 of imd_pack when A goes through a pack)
+                gpu_launches=(int(low["kernel_launches"]) + (4 if rankc is not None else 0)) * args.steps * world,
                 clocks=clocks,
                 phases_ms=phase_ms,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peak_tops, unit="TOP/s (int8)",

@@ -345,7 +345,8 @@ IMD_API unsigned int imd_test_device_error(void) {
 }
 
 /* Benchmark-only phase timing: enable with an event capacity (0 disables); read sums the milliseconds
- * per phase tag since the last read (1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate). */
+ * per phase tag since the last read (1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate,
+ * 6 imd_pack). */
 IMD_API int imd_prof_enable(int capacity) { return imd::profile_enable(capacity); }
 IMD_API int imd_prof_read(float* ms_by_tag, int tags) { return imd::profile_read(ms_by_tag, tags); }
 

@@ -65,7 +65,7 @@ int& gemm_band_mb();
 // Benchmark hook: int8 ops per second of back-to-back tcgen05.mma.kind::i8 with no loads.
 double mma_probe_tops(int pair, int sms);
 
-// Benchmark-only phase timing (tags: 1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate path).
+// Benchmark-only phase timing (tags: 1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate path, 6 imd_pack).
 int profile_enable(int capacity);
 int profile_read(float* ms_by_tag, int tags);
 

@@ -849,6 +849,7 @@ imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const 
   if (layout.total == 0) return IMD_STATUS_SUCCESS;
   uint8_t* out = static_cast<uint8_t*>(packed);
   int64_t* vec = static_cast<int64_t*>(ws);
+  mark(0, stream);
   VecParams vp;
   vp.modes = e.modes;
   vp.m = e.m, vp.n = 0, vp.k = e.k, vp.b = e.b;
@@ -885,6 +886,7 @@ imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const 
   if (!launch_residues(e, tables, o, sigma, reinterpret_cast<int8_t*>(out + layout.offset[2]), 0,
                        e.N, stream))
     return IMD_STATUS_CUDA_ERROR;
+  mark(6, stream);
   return IMD_STATUS_SUCCESS;
 }
 

@@ -10,7 +10,9 @@ single-GPU call.
 Ownership before the call: A is cut in `world` equal pieces along its label `lb` (a label of A and
 C), B likewise along `la`; the pieces of a slab belong to exactly the ranks that consume it.
 `gather` brings them together with one NCCL all-gather per operand inside the rank's grid column
-(A) or row (B). The pieces land
+(A) or row (B); `RankContraction` is the whole step of one rank: both gathers on a side stream,
+operand A packed (`imd_pack`) as soon as its slab is complete and while B's slab is still arriving,
+then `imd_contract_packed`. The pieces land
 side by side in one buffer [pieces, ...piece shape]; instead of copying them into a dense slab the
 plan describes that buffer directly by splitting the label in two (piece index, index inside the
 piece), which the strided-tensor front end handles at no cost.
@@ -128,3 +130,63 @@ def gather(part, shard_a, shard_b, out_a, out_b, groups, dist):
             out[0].copy_(shard)
         else:
             dist.all_gather_into_tensor(out.view(-1), shard.contiguous().view(-1), group=grp)
+
+
+class RankContraction:
+    """One rank's step of the partitioned contraction: exchange + compute, overlapped.
+
+        side stream   all-gather A | all-gather B
+        main stream                | imd_pack(A) ........ | imd_contract_packed(A packed, B in line)
+
+    Owns the gathered buffers, the packed buffer and the workspaces (allocated here, once).
+    `dist` is torch.distributed (initialised) and `groups` = make_groups(world, dist); with
+    world = 1 the gathers are plain copies. Device memory and streams come from torch."""
+
+    def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None):
+        import torch
+        from . import device as _dev
+        self._torch, self.part, self.dist = torch, part, dist
+        self.groups = groups if groups is not None else ({part.rb: None}, {part.ra: None})
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.A = torch.empty(part.gathered_shape(0), dtype=torch.float64, device=dev)
+        self.B = torch.empty(part.gathered_shape(1), dtype=torch.float64, device=dev)
+        self.spec, _, _, lc = part.plan_layouts()
+        self.tile_shape = lc.shape
+        proto = torch.empty(lc.shape, dtype=torch.float64, device=dev)
+        self.pack = _dev.Pack(_dev.pack_spec(self.spec, self.A, self.B, proto, operand=0, N=N, g=g,
+                                             rounding=rounding, lib=lib), lib=lib)
+        self.plan = _dev.Plan(self.spec, self.A, self.B, proto, N=N, g=g, rounding=rounding,
+                              packs=(self.pack, None), lib=lib)
+        del proto
+        nbytes = lambda n: torch.empty(max(int(n), 1), dtype=torch.uint8, device=dev)
+        self.packed, self.pack_ws = nbytes(self.pack.pack_bytes), nbytes(self.pack.workspace_bytes)
+        self.ws = nbytes(self.plan.workspace_bytes)
+        self.side = torch.cuda.Stream(dev)
+
+    def _gather(self, out, shard, grp):
+        if grp is None:
+            out[0].copy_(shard, non_blocking=True)
+        else:
+            self.dist.all_gather_into_tensor(out.view(-1), shard.contiguous().view(-1), group=grp)
+
+    def __call__(self, shard_a, shard_b, C, alpha=1.0, beta=0.0):
+        """C (this rank's tile, shape `tile_shape`) <- alpha A.B + beta C from the rank's pieces of
+        A and B; enqueued on the current stream (and a side stream that joins it)."""
+        torch = self._torch
+        main = torch.cuda.current_stream()
+        cols, rows = self.groups
+        self.side.wait_event(main.record_event())
+        with torch.cuda.stream(self.side):
+            self._gather(self.A, shard_a, cols[self.part.rb])
+            a_in = self.side.record_event()
+            self._gather(self.B, shard_b, rows[self.part.ra])
+            b_in = self.side.record_event()
+        main.wait_event(a_in)
+        self.pack.pack(self.A, self.packed, workspace=self.pack_ws, stream=main)
+        main.wait_event(b_in)
+        return self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
+                                  stream=main, packed=(self.packed, None))
+
+    def close(self):
+        self.plan.close()
+        self.pack.close()

@@ -1,0 +1,31 @@
+"""The rank-level step of the partitioned contraction on one GPU (world = 1: the gathers are
+copies; the pack-while-gathering path and the split-label plan are the same as with more ranks)."""
+import numpy as np
+import pytest
+
+from golden_util import same_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def test_rank_contraction_world_1_equals_plain_call():
+    import torch
+    import immerdink_b200 as imd
+    from immerdink_b200 import dist as idist
+    spec = "kjbc,kiac->abij"
+    e = dict(a=6, b=4, c=9, i=5, j=3, k=4)
+    part = idist.Partition(spec, e, 1, 0, "a", "b")
+    rng = np.random.default_rng(11)
+    A = torch.from_numpy(rng.standard_normal(part.shard_shape(0))).cuda()
+    B = torch.from_numpy(rng.standard_normal(part.shard_shape(1))).cuda()
+    A[0, 1, 2, 3] = float("nan")
+    rc = idist.RankContraction(part, N=14, g=7)
+    C1 = torch.full(rc.tile_shape, 3.0, dtype=torch.float64, device="cuda")
+    for _ in range(2):
+        rc(A, B, C1, alpha=0.5, beta=0.0)
+    C0 = torch.zeros(tuple(e[c] for c in "abij"), dtype=torch.float64, device="cuda")
+    ws = torch.empty(imd.workspace_size(spec, A, B, C0, N=14, g=7), dtype=torch.uint8, device="cuda")
+    imd.contract(spec, A, B, C0, alpha=0.5, N=14, g=7, workspace=ws)
+    torch.cuda.synchronize()
+    assert same_bits(C1.reshape(C0.shape).cpu().numpy(), C0.cpu().numpy())
+    rc.close()
