@@ -404,6 +404,9 @@ def run_ours(args, rank, world, local_rank):
     peak_tops = 2.0 * bf16 if bf16 else 2.0 * 1590.0
     lib.lib.imd_prof_mma_peak.restype = C.c_double
     probe_tops = lib.lib.imd_prof_mma_peak(1) / 1e12
+    # DRAM bytes (read + write) of ONE GEMM launch (one residue group), from single-pass ncu captures
+    # of this command (dram__bytes_read.sum + dram__bytes_write.sum); None where not captured.
+    gemm_traffic = {"cc8000": 2.95e9, "cc4000": 3.16e8}.get(args.workload) if world == 1 else None
     gemm_ops = 2.0 * prob.N * low["b"] * low["m"] * low["n"] * low["k"]
     achieved = gemm_ops / (phase_ms["gemm"] * 1e-3) / 1e12 if phase_ms["gemm"] > 0 else 0.0
     line = dict(metric="fp64_equivalent_tflops", value=flops / (ms_max * 1e-3) / 1e12, unit="TFLOPS-eq",
@@ -427,11 +430,14 @@ def run_ours(args, rank, world, local_rank):
                 clocks=clocks,
                 phases_ms=phase_ms,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peak_tops, unit="TOP/s (int8)",
-                              frac=achieved / peak_tops, traffic=None,
+                              frac=achieved / peak_tops, traffic=gemm_traffic,
                               peak_probe=probe_tops,
                               note=("peak = 2 x measured burst dense bf16 (of measured)" if bf16
                                     else "peak = 2 x 1590 TFLOP/s bf16 (of fallback)") +
-                              "; peak_probe = back-to-back tcgen05.mma.kind::i8 on this GPU, no loads"),
+                              "; peak_probe = back-to-back tcgen05.mma.kind::i8 on this GPU, no loads; achieved = "
+                              "2 N b m n k int8 ops of the call / time of its GEMM launches; traffic = DRAM "
+                              "bytes of one GEMM launch (algorithmic: both operands' planes once + product "
+                              "planes once = 1.34e9 at cc8000)"),
                 device_error=int(err))
     if world == 1 and not args.no_cpu:
         # DGEMM on the same GPU, same GEMM view
