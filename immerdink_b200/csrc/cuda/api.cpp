@@ -329,6 +329,10 @@ IMD_API int imd_test_gemm_band_mb(int mb) {
   if (mb > 0) imd::gemm_band_mb() = mb;
   return imd::gemm_band_mb();
 }
+IMD_API int imd_test_gemm_l2_hints(int on) {
+  if (on >= 0) imd::gemm_l2_hints() = on;
+  return imd::gemm_l2_hints();
+}
 IMD_API int imd_test_gemm_variant(int v) {
   imd::gemm_variant() = v;
   return 0;

@@ -77,12 +77,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// L2 eviction policy of an operand load.
+__device__ __forceinline__ uint64_t l2_policy(int kind) {  // 0 normal, 1 evict last, 2 evict first
+  uint64_t pol;
+  if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  else if (kind == 2) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2) {
+                                            int c0, int c1, int c2, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+        "l"(policy)
       : "memory");
 }
 
@@ -131,6 +141,7 @@ struct GemmParams {
   int32_t tiles_m, tiles_n;
   int32_t k_blocks;
   int32_t band_rows;  // tile rows walked together (see tile_of)
+  int32_t l2_hints;   // eviction policy of A's loads (bits 0-1) and B's (bits 2-3): 0 normal, 1 last, 2 first
   uint8_t* W;
   unsigned int* error_word;
 };
@@ -250,6 +261,7 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       uint32_t phase = 0;
       uint32_t issued = 0;  // bit s: a load into stage s is (or was) in flight
       bool okay = true;
+      const uint64_t pol_a = l2_policy(p.l2_hints & 3), pol_b = l2_policy((p.l2_hints >> 2) & 3);
       for (int64_t w = blockIdx.x; w < total && okay; w += gridDim.x) {
         const TileCoord c = tile_of(p, w);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -260,8 +272,8 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           mbar_expect_tx(full(stage), kStageBytes);
           const uint32_t dst = tiles + stage * kStageBytes;
           const int kx = p.s.k0 + kb * kTileK;
-          tma_load_3d(dst, &map_a, full(stage), kx, c.tm * kTileM, c.plane);
-          tma_load_3d(dst + kBytesA, &map_b, full(stage), kx, c.tn * kTileN, c.plane);
+          tma_load_3d(dst, &map_a, full(stage), kx, c.tm * kTileM, c.plane, pol_a);
+          tma_load_3d(dst + kBytesA, &map_b, full(stage), kx, c.tn * kTileN, c.plane, pol_b);
           issued |= 1u << stage;
           if (++stage == kStages) {
             stage = 0;
@@ -405,11 +417,13 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
                : "memory");
 }
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map,
-                                                 uint32_t leader_bar, int c0, int c1, int c2) {
+                                                 uint32_t leader_bar, int c0, int c1, int c2,
+                                                 uint64_t policy) {
   asm volatile(
       "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
+      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2),
+        "l"(policy)
       : "memory");
 }
 // Arrives on the barrier at this shared-memory offset in the CTAs of `mask` (bit r = CTA rank r)
@@ -499,6 +513,7 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool okay = true;
+      const uint64_t pol_a = l2_policy(p.l2_hints & 3), pol_b = l2_policy((p.l2_hints >> 2) & 3);
       for (int64_t w = first; w < total && okay; w += step) {
         const TileCoord c = pair_tile_of(p, w);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -511,9 +526,9 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t dst = tiles + stage * kPairStageBytes;
           const int kx = p.s.k0 + kb * kTileK;
           tma_load_3d_pair(dst, &map_a, leader_full, kx, c.tm * 256 + static_cast<int>(rank) * 128,
-                           c.plane);
+                           c.plane, pol_a);
           tma_load_3d_pair(dst + kBytesA, &map_b, leader_full, kx,
-                           c.tn * 256 + static_cast<int>(rank) * 128, c.plane);
+                           c.tn * 256 + static_cast<int>(rank) * 128, c.plane, pol_b);
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
@@ -730,6 +745,7 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
     p.band_rows = static_cast<int32_t>(rows < p.tiles_m ? rows : p.tiles_m);
     if (p.band_rows < 1) p.band_rows = 1;
   }
+  p.l2_hints = gemm_l2_hints();
   p.W = W;
   p.error_word = info.error_word;
   const int64_t total = static_cast<int64_t>(s.planes) * p.tiles_m * p.tiles_n;
@@ -770,6 +786,14 @@ double mma_probe_tops(int pair, int sms) {
 
 int& gemm_band_mb() {
   static int v = 32;  // tuning hook: MB of A rows kept L2-resident by the tile order
+  return v;
+}
+
+int& gemm_l2_hints() {
+  // Both operands "evict last": they are re-used across the band, the product planes written by
+  // the epilogue are not. Measured: about 2 % less launch time than without hints; "evict first"
+  // on the streamed operand multiplies the DRAM reads (its rows are still needed by the band).
+  static int v = 5;
   return v;
 }
 

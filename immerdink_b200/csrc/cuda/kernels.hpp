@@ -62,6 +62,8 @@ bool& use_reference_gemm();
 int& gemm_variant();
 // Tuning hook: MB of operand A's tile rows that the tile order keeps resident in L2 (default 32).
 int& gemm_band_mb();
+// Tuning hook: L2 eviction hints of the GEMM's operand loads (1: keep A's band, stream B).
+int& gemm_l2_hints();
 // Benchmark hook: int8 ops per second of back-to-back tcgen05.mma.kind::i8 with no loads.
 double mma_probe_tops(int pair, int sms);
 
