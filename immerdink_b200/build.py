@@ -19,7 +19,8 @@ HOST_LIB = os.path.join(HERE, "libimmerdink_host.so")
 CUDA_LIB = os.path.join(HERE, "libimmerdink.so")
 
 HOST_SOURCES = [os.path.join(CSRC, "host", f)
-                for f in ("lowering.cpp", "plan.cpp", "pack.cpp", "host_api.cpp", "accuracy.cpp")]
+                for f in ("lowering.cpp", "plan.cpp", "pack.cpp", "host_api.cpp", "accuracy.cpp", "perf.cpp",
+                          "perf_text.cpp")]
 CUDA_SOURCES = [os.path.join(CSRC, "cuda", f)
                 for f in ("api.cpp", "pipeline.cu", "gemm_tcgen05.cu")]
 

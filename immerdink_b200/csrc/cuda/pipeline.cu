@@ -525,8 +525,15 @@ unsigned int grid_for(int64_t items, int64_t cap = int64_t{1} << 30) {
 
 bool launched() { return cudaPeekAtLastError() == cudaSuccess; }
 
-int scale_lg_rt(bool rows_fast, int64_t k) {
-  if (rows_fast) return 5;  // 32 rows x 8 K lanes
+// log2 of the rows a CTA of the scale kernel owns. Rows contiguous: 32 rows x 8 K lanes (256-byte
+// segments per K step), fewer rows (down to 4: one 32-byte sector per step) and more K lanes when
+// that leaves fewer than two CTAs per SM. K contiguous: as many K lanes as k can feed.
+int scale_lg_rt(bool rows_fast, int64_t k, int64_t rows_total) {
+  if (rows_fast) {
+    int lg = 5;
+    while (lg > 2 && (rows_total >> lg) < 2 * kDefaultSms) --lg;
+    return lg;
+  }
   int lanes = 1;
   while (lanes < 256 && lanes < k) lanes <<= 1;
   int lg = 0;
@@ -668,7 +675,7 @@ bool launch_scale(const ExecPlan& e, const OperandView& o, int16_t* sigma, uint8
   p.batches = e.b;
   p.k = e.k;
   p.rows_fast = o.rows_fast;
-  p.lg_rt = scale_lg_rt(o.rows_fast, e.k);
+  p.lg_rt = scale_lg_rt(o.rows_fast, e.k, o.rows * e.b);
   p.lhs_shift = e.lhs_shift;
   p.rhs = e.rhs;
   p.sigma = sigma;

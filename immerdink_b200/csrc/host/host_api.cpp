@@ -294,44 +294,4 @@ imd_status_t imd_lowering_packed(const imd_tensor_t* A, const imd_tensor_t* B,
   return lowering_impl(A, B, C, options, packing, out);
 }
 
-/* ---- performance model: not shipped for this engine yet (see the header) ------------------- */
-const char* imd_perf_kernel_name(int32_t) { return nullptr; }
-imd_status_t imd_perf_calib_default(imd_perf_calib_t*) { return IMD_STATUS_NOT_SUPPORTED; }
-imd_status_t imd_perf_calib_parse(const char*, size_t, imd_perf_calib_t*, int32_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-imd_status_t imd_perf_calib_load(const char*, imd_perf_calib_t*, int32_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-imd_status_t imd_perf_calib_parse_ex(const char*, size_t, imd_perf_calib_t*, imd_perf_calib_error_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-imd_status_t imd_perf_calib_load_ex(const char*, imd_perf_calib_t*, imd_perf_calib_error_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-imd_status_t imd_perf_calib_default_ex(imd_perf_calib_t*, imd_perf_calib_error_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-const char* imd_perf_calib_error_name(int32_t) { return nullptr; }
-imd_status_t imd_perf_calib_format(const imd_perf_calib_t*, char*, size_t, size_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-const char* imd_perf_class_name(int32_t) { return nullptr; }
-const char* imd_perf_param_name(int32_t, int32_t) { return nullptr; }
-const char* imd_perf_phase_name(int32_t) { return nullptr; }
-imd_status_t imd_perf_predict(const imd_tensor_t*, const imd_tensor_t*, const imd_tensor_t*,
-                              const imd_options_t*, const imd_packing_t*, const imd_perf_request_t*,
-                              const imd_perf_calib_t*, imd_perf_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-imd_status_t imd_perf_predict_pack(const imd_pack_desc_t*, const imd_perf_request_t*,
-                                   const imd_perf_calib_t*, imd_perf_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-imd_status_t imd_perf_rank(const imd_tensor_t*, const imd_tensor_t*, const imd_tensor_t*,
-                           const imd_options_t*, const imd_perf_rank_request_t*,
-                           const imd_perf_calib_t*, imd_perf_candidate_t*, int32_t, int32_t*) {
-  return IMD_STATUS_NOT_SUPPORTED;
-}
-
 }  // extern "C"

@@ -445,3 +445,292 @@ def min_moduli(spec, extents=None, *, target, rounding="RN", mode="EMULATE", n_l
     if st:
         raise ImmerdinkError(st, "imd_err_min_moduli")
     return _err_dict(out)
+
+
+# ------------------------------------------------------------------ performance model
+PERF_REGIMES = {"DEFAULT": 0, "BURST": 1, "SUSTAINED": 2}
+PERF_CACHES = {"COLD": 0, "WARM": 1, "REPEAT": 2, "CLEAN": 3}
+PERF_ORDERS = {"TIME": 0, "TIES_BY_FOOTPRINT": 1}
+_PERF_VEC = {"GENERATE": 1, "RESIDENT": 2}
+_PERF_PACK = {"NONE": 1, "A": 2, "B": 4, "AB": 8}
+PERF_CLASS_COUNT, PERF_PHASE_COUNT, PERF_KERNEL_COUNT, PERF_MAX_PARAMS = 12, 13, 90, 6
+
+
+class CPerfKernel(C.Structure):
+    _fields_ = [("resident", C.c_int32), ("regs", C.c_int32), ("smem_bytes", C.c_int32),
+                ("threads", C.c_int32)]
+
+
+class CPerfCalib(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("format", C.c_int32), ("sm_count", C.c_int32),
+                ("reserved", C.c_int32), ("peak_dram_bytes_per_s", C.c_double),
+                ("peak_int8_ops_per_s", C.c_double), ("peak_fp64_flops_per_s", C.c_double),
+                ("l2_bytes", C.c_double), ("gpu", C.c_char * 64), ("date", C.c_char * 32),
+                ("version", C.c_char * 64), ("clocks", C.c_char * 128), ("notes", C.c_char * 128),
+                ("param", C.c_double * 96), ("kernel", CPerfKernel * 128),
+                ("clock_eff_mhz", C.c_double), ("clock_min_mhz", C.c_double),
+                ("power_cap_w", C.c_double), ("power_idle_w", C.c_double),
+                ("energy_tc_pj", C.c_double), ("energy_alu_pj", C.c_double),
+                ("energy_byte_pj", C.c_double), ("energy_gamma", C.c_double),
+                ("warm_l2_bytes", C.c_double), ("warm_l2byte_ns", C.c_double),
+                ("band_call", (C.c_double * 2) * 3), ("band_class", (C.c_double * 2) * 16),
+                ("tie_ratio", C.c_double), ("energy_byte_f_pj", C.c_double),
+                ("pack_l2_hit_bytes", C.c_double), ("clock_boost_mhz", C.c_double),
+                ("power_act_w", C.c_double), ("power_act_gap_us", C.c_double),
+                ("energy_dram_pj", C.c_double), ("warm_call_ns", C.c_double),
+                ("warm_clean_byte_ns", C.c_double), ("pack_l2_planes", C.c_double)]
+
+
+class CPerfCalibError(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("line", C.c_int32), ("reason", C.c_int32),
+                ("reserved", C.c_int32), ("key", C.c_char * 64), ("message", C.c_char * 192)]
+
+
+class CPerfRequest(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("flags", C.c_int32), ("k4_config", C.c_int32),
+                ("reserved", C.c_int32), ("eps_fraction", C.c_double), ("regime", C.c_int32),
+                ("cache", C.c_int32), ("clock_mhz", C.c_double), ("accuracy", C.POINTER(CErrRequest))]
+
+
+class CPerfPhase(C.Structure):
+    _fields_ = [("phase", C.c_int32), ("cls", C.c_int32), ("launches", C.c_int64),
+                ("time_s", C.c_double), ("bytes", C.c_double), ("ops", C.c_double),
+                ("bound_s", C.c_double), ("x", C.c_double * 6)]
+
+
+class CPerf(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("status", C.c_int32), ("dispatch", C.c_int32),
+                ("k4_config", C.c_int32), ("sm_count", C.c_int32), ("num_phases", C.c_int32),
+                ("time_s", C.c_double), ("bound_s", C.c_double), ("flops_eq", C.c_double),
+                ("tflops_eq", C.c_double), ("eps_s", C.c_double), ("eps_fraction", C.c_double),
+                ("kernel_launches", C.c_int64), ("workspace_bytes", C.c_uint64),
+                ("plan_device_bytes", C.c_uint64), ("pack_bytes", C.c_uint64),
+                ("pack_ws_bytes", C.c_uint64), ("phase", CPerfPhase * 16), ("regime", C.c_int32),
+                ("cache", C.c_int32), ("clock_mhz", C.c_double), ("power_w", C.c_double),
+                ("warm_bytes", C.c_double), ("time_lo_s", C.c_double), ("time_hi_s", C.c_double),
+                ("phase_lo_s", C.c_double * 16), ("phase_hi_s", C.c_double * 16),
+                ("err_bound", C.c_double), ("err_typical", C.c_double), ("err_status", C.c_int32),
+                ("err_metric", C.c_int32)]
+
+
+class CRankRequest(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("candidate_size", C.c_uint32),
+                ("num_moduli_count", C.c_int32), ("residue_group_count", C.c_int32),
+                ("num_moduli", C.POINTER(C.c_int32)), ("residue_groups", C.POINTER(C.c_int32)),
+                ("vec_modes", C.c_int32), ("pack_modes", C.c_int32), ("reuse", C.c_int32),
+                ("flags", C.c_int32), ("budget_bytes", C.c_uint64), ("eps_fraction", C.c_double),
+                ("regime", C.c_int32), ("cache", C.c_int32), ("order", C.c_int32),
+                ("reserved", C.c_int32), ("clock_mhz", C.c_double),
+                ("accuracy", C.POINTER(CErrRequest))]
+
+
+class CCandidate(C.Structure):
+    _fields_ = [("num_moduli", C.c_int32), ("residue_group", C.c_int32), ("vec_mode", C.c_int32),
+                ("packed", C.c_int32), ("status", C.c_int32), ("feasible", C.c_int32),
+                ("k4_config", C.c_int32), ("dispatch", C.c_int32), ("time_s", C.c_double),
+                ("contract_s", C.c_double), ("pack_s", C.c_double), ("tflops_eq", C.c_double),
+                ("eps_s", C.c_double), ("eps_fraction", C.c_double), ("workspace_bytes", C.c_uint64),
+                ("plan_device_bytes", C.c_uint64), ("pack_bytes", C.c_uint64),
+                ("pack_ws_bytes", C.c_uint64), ("total_bytes", C.c_uint64),
+                ("kernel_launches", C.c_int64), ("time_lo_s", C.c_double), ("time_hi_s", C.c_double),
+                ("clock_mhz", C.c_double), ("power_w", C.c_double), ("tie", C.c_int32),
+                ("raw_rank", C.c_int32), ("err_bound", C.c_double), ("err_typical", C.c_double),
+                ("err_status", C.c_int32), ("infeasible", C.c_int32)]
+
+
+assert (C.sizeof(CPerfCalib), C.sizeof(CPerf), C.sizeof(CCandidate), C.sizeof(CRankRequest),
+        C.sizeof(CPerfRequest), C.sizeof(CPerfCalibError)) == (3744, 1976, 192, 96, 48, 272)
+
+
+class CalibrationError(ValueError):
+    """A calibration text that does not parse: .line, .reason (name), .key."""
+
+    def __init__(self, err):
+        self.line, self.key = err.line, err.key.decode()
+        self.reason = err.reason
+        super().__init__(err.message.decode() or "calibration rejected")
+
+
+def _names(fn, count):
+    fn.restype = C.c_char_p
+    return [fn(i).decode() for i in range(count)]
+
+
+def phase_names(lib=None):
+    return _names((lib or load()).lib.imd_perf_phase_name, PERF_PHASE_COUNT)
+
+
+def class_names(lib=None):
+    return _names((lib or load()).lib.imd_perf_class_name, PERF_CLASS_COUNT)
+
+
+def kernel_names(lib=None):
+    return _names((lib or load()).lib.imd_perf_kernel_name, PERF_KERNEL_COUNT)
+
+
+def param_names(lib=None):
+    """{class name: [parameter names by slot (None: unused)]}."""
+    L = (lib or load()).lib
+    L.imd_perf_param_name.restype = C.c_char_p
+    L.imd_perf_param_name.argtypes = [C.c_int32, C.c_int32]
+    out = {}
+    for ci, cn in enumerate(class_names(lib)):
+        out[cn] = [(lambda v: None if v is None else v.decode())(L.imd_perf_param_name(ci, j))
+                   for j in range(PERF_MAX_PARAMS)]
+    return out
+
+
+def calib_default(lib=None):
+    """The shipped calibration (B200) as a CPerfCalib struct."""
+    L = (lib or load()).lib
+    c, e = CPerfCalib(), CPerfCalibError()
+    c.struct_size, e.struct_size = C.sizeof(CPerfCalib), C.sizeof(CPerfCalibError)
+    L.imd_perf_calib_default_ex.argtypes = [C.POINTER(CPerfCalib), C.POINTER(CPerfCalibError)]
+    if L.imd_perf_calib_default_ex(C.byref(c), C.byref(e)):
+        raise CalibrationError(e)
+    return c
+
+
+def calib_parse(text, lib=None):
+    """Calibration text -> CPerfCalib; CalibrationError with line, reason and key."""
+    L = (lib or load()).lib
+    raw = text.encode() if isinstance(text, str) else bytes(text)
+    c, e = CPerfCalib(), CPerfCalibError()
+    c.struct_size, e.struct_size = C.sizeof(CPerfCalib), C.sizeof(CPerfCalibError)
+    L.imd_perf_calib_parse_ex.argtypes = [C.c_char_p, C.c_size_t, C.POINTER(CPerfCalib),
+                                          C.POINTER(CPerfCalibError)]
+    if L.imd_perf_calib_parse_ex(raw, len(raw), C.byref(c), C.byref(e)):
+        raise CalibrationError(e)
+    return c
+
+
+def calib_load(path, lib=None):
+    L = (lib or load()).lib
+    c, e = CPerfCalib(), CPerfCalibError()
+    c.struct_size, e.struct_size = C.sizeof(CPerfCalib), C.sizeof(CPerfCalibError)
+    L.imd_perf_calib_load_ex.argtypes = [C.c_char_p, C.POINTER(CPerfCalib), C.POINTER(CPerfCalibError)]
+    if L.imd_perf_calib_load_ex(os.fsencode(path), C.byref(c), C.byref(e)):
+        raise CalibrationError(e)
+    return c
+
+
+def calib_format(calib=None, lib=None):
+    """Canonical text of a calibration (None: the shipped one); parse(format(c)) == c."""
+    L = (lib or load()).lib
+    L.imd_perf_calib_format.argtypes = [C.POINTER(CPerfCalib), C.c_char_p, C.c_size_t,
+                                        C.POINTER(C.c_size_t)]
+    n = C.c_size_t(0)
+    ptr = None if calib is None else C.byref(calib)
+    st = L.imd_perf_calib_format(ptr, None, 0, C.byref(n))
+    if st not in (0, 4):
+        raise ImmerdinkError(st, "imd_perf_calib_format")
+    buf = C.create_string_buffer(n.value + 1)
+    st = L.imd_perf_calib_format(ptr, buf, n.value + 1, C.byref(n))
+    if st:
+        raise ImmerdinkError(st, "imd_perf_calib_format")
+    return buf.value.decode()
+
+
+def _perf_dict(r, lib):
+    ph, cl = phase_names(lib), class_names(lib)
+    phases = [dict(phase=ph[p.phase], cls=cl[p.cls], launches=p.launches, time_s=p.time_s,
+                   bytes=p.bytes, ops=p.ops, bound_s=p.bound_s, x=list(p.x),
+                   lo_s=r.phase_lo_s[i], hi_s=r.phase_hi_s[i])
+              for i, p in enumerate(r.phase[:r.num_phases])]
+    return dict(status=STATUS[r.status], dispatch=DISPATCH[r.dispatch], sm_count=r.sm_count,
+                time_s=r.time_s, time_lo_s=r.time_lo_s, time_hi_s=r.time_hi_s, bound_s=r.bound_s,
+                flops_eq=r.flops_eq, tflops_eq=r.tflops_eq, kernel_launches=r.kernel_launches,
+                workspace_bytes=r.workspace_bytes, plan_device_bytes=r.plan_device_bytes,
+                pack_bytes=r.pack_bytes, pack_ws_bytes=r.pack_ws_bytes, phases=phases,
+                regime=r.regime, cache=r.cache, clock_mhz=r.clock_mhz, power_w=r.power_w,
+                err_bound=r.err_bound, err_typical=r.err_typical,
+                err_status=ERR_STATUS[r.err_status])
+
+
+def _perf_request(beta, alpha_zero, regime, cache, clock_mhz, accuracy):
+    flags = (1 if beta else 0) | (2 if alpha_zero else 0)
+    acc = None if accuracy is None else C.pointer(accuracy)
+    return CPerfRequest(C.sizeof(CPerfRequest), flags, -1, 0, -1.0, PERF_REGIMES[regime],
+                        PERF_CACHES[cache], float(clock_mhz), acc)
+
+
+def predict(spec, extents=None, *, N, g=0, rounding="RN", mode="EMULATE", vec_mode="GENERATE",
+            strides=None, packing=None, beta=False, alpha_zero=False, regime="DEFAULT",
+            cache="COLD", clock_mhz=0.0, accuracy=None, calib=None, lib=None):
+    """imd_perf_predict: predicted time of one imd_contract per phase and in total, as a dict. A
+    plan-time status comes back in ["status"]; a bad argument raises. packing = (PackSpec or None,
+    PackSpec or None); accuracy: a CErrRequest; calib: a CPerfCalib (None: the shipped one)."""
+    L, ds, o = _call(spec, extents, strides, lib, options(N, g, rounding, mode, vec_mode))
+    cp, keep = _packing(packing)
+    req = _perf_request(beta, alpha_zero, regime, cache, clock_mhz, accuracy)
+    r = CPerf()
+    r.struct_size = C.sizeof(CPerf)
+    L.lib.imd_perf_predict.argtypes = [C.POINTER(CTensor)] * 3 + [
+        C.POINTER(COptions), C.POINTER(CPacking), C.POINTER(CPerfRequest), C.POINTER(CPerfCalib),
+        C.POINTER(CPerf)]
+    st = L.lib.imd_perf_predict(ds[0].t, ds[1].t, ds[2].t, o, None if cp is None else C.byref(cp),
+                                C.byref(req), None if calib is None else C.byref(calib), C.byref(r))
+    if st and r.status == 0:
+        raise ImmerdinkError(st, "imd_perf_predict")
+    return _perf_dict(r, L)
+
+
+def predict_pack(pack, *, regime="DEFAULT", cache="COLD", clock_mhz=0.0, calib=None, lib=None):
+    """imd_perf_predict_pack: predicted time of one imd_pack of a PackSpec."""
+    L = lib or load()
+    cs = CPackSpec(pack)
+    req = _perf_request(False, False, regime, cache, clock_mhz, None)
+    r = CPerf()
+    r.struct_size = C.sizeof(CPerf)
+    L.lib.imd_perf_predict_pack.argtypes = [C.POINTER(CPackDesc), C.POINTER(CPerfRequest),
+                                            C.POINTER(CPerfCalib), C.POINTER(CPerf)]
+    st = L.lib.imd_perf_predict_pack(C.byref(cs.d), C.byref(req),
+                                     None if calib is None else C.byref(calib), C.byref(r))
+    if st and r.status == 0:
+        raise ImmerdinkError(st, "imd_perf_predict_pack")
+    return _perf_dict(r, L)
+
+
+def rank(spec, extents=None, *, N, g=None, vec_modes=("GENERATE",), packs=("NONE",), reuse=1,
+         budget=0, beta=False, rounding="RN", mode="EMULATE", strides=None, order="TIME",
+         regime="DEFAULT", cache="COLD", clock_mhz=0.0, accuracy=None, calib=None, lib=None):
+    """imd_perf_rank: the candidates N x g x vec mode x packs ranked by predicted time inside a
+    device-memory budget (bytes; 0 = none), as a list of dicts. N: an int or a list; g: None
+    (every g in 1..N) or a list; packs: any of "NONE", "A", "B", "AB"."""
+    Ns = [int(N)] if hasattr(N, "__index__") else [int(x) for x in N]
+    gs = [] if g is None else ([int(g)] if isinstance(g, int) else [int(x) for x in g])
+    L, ds, o = _call(spec, extents, strides, lib, options(Ns[0], 0, rounding, mode, "GENERATE"))
+    narr = (C.c_int32 * max(len(Ns), 1))(*Ns)
+    garr = (C.c_int32 * max(len(gs), 1))(*gs)
+    req = CRankRequest(C.sizeof(CRankRequest), C.sizeof(CCandidate), len(Ns), len(gs),
+                       C.cast(narr, C.POINTER(C.c_int32)),
+                       C.cast(garr, C.POINTER(C.c_int32)) if gs else None,
+                       sum(_PERF_VEC[v] for v in set(vec_modes)),
+                       sum(_PERF_PACK[p] for p in set(packs)), int(reuse), 1 if beta else 0,
+                       int(budget), -1.0, PERF_REGIMES[regime], PERF_CACHES[cache],
+                       PERF_ORDERS[order], 0, float(clock_mhz),
+                       None if accuracy is None else C.pointer(accuracy))
+    L.lib.imd_perf_rank.argtypes = [C.POINTER(CTensor)] * 3 + [
+        C.POINTER(COptions), C.POINTER(CRankRequest), C.POINTER(CPerfCalib), C.POINTER(CCandidate),
+        C.c_int32, C.POINTER(C.c_int32)]
+    cal = None if calib is None else C.byref(calib)
+    count = C.c_int32(0)
+    st = L.lib.imd_perf_rank(ds[0].t, ds[1].t, ds[2].t, o, C.byref(req), cal, None, 0, C.byref(count))
+    if st:
+        raise ImmerdinkError(st, "imd_perf_rank")
+    out = (CCandidate * max(count.value, 1))()
+    st = L.lib.imd_perf_rank(ds[0].t, ds[1].t, ds[2].t, o, C.byref(req), cal, out, count.value,
+                             C.byref(count))
+    if st:
+        raise ImmerdinkError(st, "imd_perf_rank")
+    vec_name = {v: k for k, v in VEC.items()}
+    return [dict(N=c.num_moduli, g=c.residue_group, vec_mode=vec_name[c.vec_mode],
+                 packs=["NONE", "A", "B", "AB"][c.packed], status=STATUS[c.status],
+                 feasible=bool(c.feasible), infeasible=c.infeasible, dispatch=DISPATCH[c.dispatch],
+                 time_s=c.time_s, contract_s=c.contract_s, pack_s=c.pack_s, tflops_eq=c.tflops_eq,
+                 workspace_bytes=c.workspace_bytes, plan_device_bytes=c.plan_device_bytes,
+                 pack_bytes=c.pack_bytes, pack_ws_bytes=c.pack_ws_bytes, total_bytes=c.total_bytes,
+                 kernel_launches=c.kernel_launches, time_lo_s=c.time_lo_s, time_hi_s=c.time_hi_s,
+                 tie=bool(c.tie), raw_rank=c.raw_rank, err_bound=c.err_bound,
+                 err_typical=c.err_typical, err_status=ERR_STATUS[c.err_status])
+            for c in out[:count.value]]

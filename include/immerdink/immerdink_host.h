@@ -260,17 +260,151 @@ IMD_API imd_status_t imd_err_min_moduli(const imd_tensor_t* A, const imd_tensor_
                                         const imd_err_request_t* request, imd_err_t* out);
 
 /* ---- Performance model. ref: immerdink_host.h:409-839 ------------------------------------
- * The symbols exist so that callers binding the whole host ABI at load time keep loading. The
- * reference's model is calibrated per kernel for its sm_89 pipeline; a B200 calibration of this
- * engine's three-kernel pipeline is not shipped yet, and every function below that would need
- * one returns IMD_STATUS_NOT_SUPPORTED (name lookups return NULL) without touching its
- * outputs. The structs are left opaque until then. */
-typedef struct imd_perf_calib_s imd_perf_calib_t;
-typedef struct imd_perf_calib_error_s imd_perf_calib_error_t;
-typedef struct imd_perf_request_s imd_perf_request_t;
-typedef struct imd_perf_s imd_perf_t;
-typedef struct imd_perf_rank_request_s imd_perf_rank_request_t;
-typedef struct imd_perf_candidate_s imd_perf_candidate_t;
+ * Predicted time of one imd_contract / imd_pack per phase and in total, and a ranking of the
+ * configurations a caller may choose (N, g, vec mode, packed operands) within a memory budget.
+ * Struct layouts, enum values, function names, argument checks and the ranking order are the
+ * reference's. The MODEL is this engine's: phases are its own kernels, the features x are
+ * computed from the plan's lowering, and the shipped calibration (NULL) is a B200 (sm_100a) one.
+ *   t_phase = sum_j param[class * 6 + j] * x[j]  (ns); GEMM class: max(terms j != 4, term j = 4).
+ * Phase -> kernel of this engine (class):
+ *   K0 "K0 vec"        k_vectors                        (k0: launch, byte)
+ *   KL_A / KL_B        k_scale of the post-swap A / B   (kl: launch, byte, op = elements)
+ *   PACK_A / PACK_B    k_residues of A / B, all groups  (pack: launch, byte, op = residues,
+ *                                                        chain = quantisations)
+ *   K4                 k_gemm_i8(_pair), all launches   (k4_128x256: round = tile rounds with a main
+ *                                                        loop too short to hide the epilogue,
+ *                                                        mac1 = MACs of the busiest SM in the
+ *                                                        other rounds incl. tile padding,
+ *                                                        byte = modelled DRAM bytes)
+ *   K5                 k_crt                            (k5: launch, byte, op = outputs x N)
+ *   DIRECT, BETA       k_direct, k_beta                 (direct: launch, byte, flop; beta)
+ *   CALL               per call and per launch host / gap term
+ *   PACK_PREP, PACK_KL, PACK_A   imd_pack: vectors + zero ranges, k_scale, k_residues (g = N)
+ * Not modelled (accepted, validated, no effect): clock regimes and the power model (the
+ * shipped calibration has power.cap_w = 0: SUSTAINED = BURST, power_w = 0), cache states
+ * (warm_bytes = 0), the K4 configurations other than 128x256 (k4_config of a request is
+ * validated and ignored: one GEMM kernel per shape class). Calibration text: format 2 only. */
+#define IMD_PERF_CALIB_FORMAT 2
+#define IMD_PERF_MAX_PARAMS 6
+#define IMD_PERF_PARAM_CAPACITY 96
+#define IMD_PERF_PARAM_KL_DROP_SLOT (IMD_PERF_PARAM_CAPACITY - 1)
+#define IMD_PERF_MAX_PHASES 16
+enum {
+  IMD_PERF_CLASS_K0 = 0, IMD_PERF_CLASS_KF = 1, IMD_PERF_CLASS_KL = 2, IMD_PERF_CLASS_PACK = 3,
+  IMD_PERF_CLASS_K4_128x256 = 4, IMD_PERF_CLASS_K4_128x128 = 5, IMD_PERF_CLASS_K4_64x128 = 6,
+  IMD_PERF_CLASS_K4_64x64 = 7, IMD_PERF_CLASS_K5 = 8, IMD_PERF_CLASS_DIRECT = 9,
+  IMD_PERF_CLASS_BETA = 10, IMD_PERF_CLASS_CALL = 11, IMD_PERF_CLASS_COUNT = 12
+};
+enum {
+  IMD_PERF_PHASE_K0 = 0, IMD_PERF_PHASE_KF = 1, IMD_PERF_PHASE_KL_A = 2, IMD_PERF_PHASE_KL_B = 3,
+  IMD_PERF_PHASE_PACK_A = 4, IMD_PERF_PHASE_PACK_B = 5, IMD_PERF_PHASE_K4 = 6,
+  IMD_PERF_PHASE_K5 = 7, IMD_PERF_PHASE_DIRECT = 8, IMD_PERF_PHASE_BETA = 9,
+  IMD_PERF_PHASE_CALL = 10, IMD_PERF_PHASE_PACK_PREP = 11, IMD_PERF_PHASE_PACK_KL = 12,
+  IMD_PERF_PHASE_COUNT = 13
+};
+enum { IMD_PERF_BETA_NONZERO = 1, IMD_PERF_ALPHA_ZERO = 2 };
+#define IMD_PERF_KERNEL_CAPACITY 128
+#define IMD_PERF_CLASS_CAPACITY 16
+enum {
+  IMD_PERF_KERNEL_K0 = 0, IMD_PERF_KERNEL_KF16 = 1, IMD_PERF_KERNEL_KF4 = 2,
+  IMD_PERF_KERNEL_KL8 = 3, IMD_PERF_KERNEL_KL4 = 4, IMD_PERF_KERNEL_PACK = 5,
+  IMD_PERF_KERNEL_ZERO_ROWS = 6, IMD_PERF_KERNEL_DIRECT = 7, IMD_PERF_KERNEL_BETA = 8,
+  IMD_PERF_KERNEL_PACK_PREP = 9, IMD_PERF_KERNEL_K4 = 10, IMD_PERF_KERNEL_K5 = 14,
+  IMD_PERF_KERNEL_COUNT = 90
+};
+typedef struct {
+  int32_t resident, regs, smem_bytes, threads;
+} imd_perf_kernel_t;
+enum { IMD_PERF_REGIME_DEFAULT = 0, IMD_PERF_REGIME_BURST = 1, IMD_PERF_REGIME_SUSTAINED = 2 };
+enum { IMD_PERF_CACHE_COLD = 0, IMD_PERF_CACHE_WARM = 1, IMD_PERF_CACHE_REPEAT = 2,
+       IMD_PERF_CACHE_CLEAN = 3 };
+enum { IMD_PERF_ORDER_TIME = 0, IMD_PERF_ORDER_TIES_BY_FOOTPRINT = 1 };
+enum { IMD_PERF_BAND_SMALL = 0, IMD_PERF_BAND_MID = 1, IMD_PERF_BAND_LARGE = 2 };
+typedef struct {
+  uint32_t struct_size;
+  int32_t format;
+  int32_t sm_count;
+  int32_t reserved;
+  double peak_dram_bytes_per_s, peak_int8_ops_per_s, peak_fp64_flops_per_s, l2_bytes;
+  char gpu[64], date[32], version[64], clocks[128], notes[128];
+  double param[IMD_PERF_PARAM_CAPACITY];
+  imd_perf_kernel_t kernel[IMD_PERF_KERNEL_CAPACITY];
+  double clock_eff_mhz, clock_min_mhz, power_cap_w, power_idle_w;
+  double energy_tc_pj, energy_alu_pj, energy_byte_pj, energy_gamma;
+  double warm_l2_bytes, warm_l2byte_ns;
+  double band_call[3][2];
+  double band_class[IMD_PERF_CLASS_CAPACITY][2];
+  double tie_ratio;
+  double energy_byte_f_pj;
+  double pack_l2_hit_bytes;
+  double clock_boost_mhz, power_act_w, power_act_gap_us, energy_dram_pj, warm_call_ns,
+      warm_clean_byte_ns, pack_l2_planes;
+} imd_perf_calib_t;
+enum { IMD_PERF_CALIB_OK = 0, IMD_PERF_CALIB_ERR_ARGUMENT = 1, IMD_PERF_CALIB_ERR_FILE = 2,
+       IMD_PERF_CALIB_ERR_SYNTAX = 3, IMD_PERF_CALIB_ERR_UNKNOWN_KEY = 4,
+       IMD_PERF_CALIB_ERR_REPEATED_KEY = 5, IMD_PERF_CALIB_ERR_VALUE = 6,
+       IMD_PERF_CALIB_ERR_TOO_LONG = 7, IMD_PERF_CALIB_ERR_MISSING_KEY = 8,
+       IMD_PERF_CALIB_ERR_FORMAT2_KEY = 9, IMD_PERF_CALIB_ERR_INCONSISTENT = 10 };
+#define IMD_PERF_CALIB_ERR_COUNT 11
+typedef struct {
+  uint32_t struct_size;
+  int32_t line, reason, reserved;
+  char key[64];
+  char message[192];
+} imd_perf_calib_error_t;
+typedef struct {
+  uint32_t struct_size;
+  int32_t flags, k4_config, reserved;
+  double eps_fraction;
+  int32_t regime, cache;
+  double clock_mhz;
+  const struct imd_err_request_s* accuracy;
+} imd_perf_request_t;
+typedef struct {
+  int32_t phase, cls;
+  int64_t launches;
+  double time_s, bytes, ops, bound_s;
+  double x[IMD_PERF_MAX_PARAMS];
+} imd_perf_phase_t;
+typedef struct {
+  uint32_t struct_size;
+  int32_t status, dispatch, k4_config, sm_count, num_phases;
+  double time_s, bound_s, flops_eq, tflops_eq, eps_s, eps_fraction;
+  int64_t kernel_launches;
+  uint64_t workspace_bytes, plan_device_bytes, pack_bytes, pack_ws_bytes;
+  imd_perf_phase_t phase[IMD_PERF_MAX_PHASES];
+  int32_t regime, cache;
+  double clock_mhz, power_w, warm_bytes, time_lo_s, time_hi_s;
+  double phase_lo_s[IMD_PERF_MAX_PHASES], phase_hi_s[IMD_PERF_MAX_PHASES];
+  double err_bound, err_typical;
+  int32_t err_status, err_metric;
+} imd_perf_t;
+enum { IMD_PERF_VEC_GENERATE = 1, IMD_PERF_VEC_RESIDENT = 2 };
+enum { IMD_PERF_PACK_NONE = 1, IMD_PERF_PACK_A = 2, IMD_PERF_PACK_B = 4, IMD_PERF_PACK_AB = 8 };
+typedef struct {
+  uint32_t struct_size, candidate_size;
+  int32_t num_moduli_count, residue_group_count;
+  const int32_t* num_moduli;
+  const int32_t* residue_groups;
+  int32_t vec_modes, pack_modes, reuse, flags;
+  uint64_t budget_bytes;
+  double eps_fraction;
+  int32_t regime, cache, order, reserved;
+  double clock_mhz;
+  const struct imd_err_request_s* accuracy;
+} imd_perf_rank_request_t;
+typedef struct {
+  int32_t num_moduli, residue_group, vec_mode, packed, status, feasible, k4_config, dispatch;
+  double time_s, contract_s, pack_s, tflops_eq, eps_s, eps_fraction;
+  uint64_t workspace_bytes, plan_device_bytes, pack_bytes, pack_ws_bytes, total_bytes;
+  int64_t kernel_launches;
+  double time_lo_s, time_hi_s, clock_mhz, power_w;
+  int32_t tie, raw_rank;
+  double err_bound, err_typical;
+  int32_t err_status, infeasible;
+} imd_perf_candidate_t;
+enum { IMD_PERF_INFEASIBLE_STATUS = 1, IMD_PERF_INFEASIBLE_BUDGET = 2,
+       IMD_PERF_INFEASIBLE_ACCURACY = 4 };
 IMD_API const char* imd_perf_kernel_name(int32_t kernel);
 IMD_API imd_status_t imd_perf_calib_default(imd_perf_calib_t* out);
 IMD_API imd_status_t imd_perf_calib_parse(const char* text, size_t length, imd_perf_calib_t* out,
