@@ -260,3 +260,37 @@ def test_packed_buffer_record():
     plan.contract(A, B, Cc, workspace=w, packed=(pb, None))
     with pytest.raises(ValueError):
         imd.Plan("ik,kj->ij", A, B, Cc, N=14, packs=(pk, None))
+
+
+@pytest.mark.parametrize("m,n,k,N,g", [(5, 20, 131500, 5, 2), (150, 40, 700, 7, 3), (16, 300, 97, 11, 4)])
+def test_packed_with_residue_groups_and_k_chunks(m, n, k, N, g):
+    """A packed buffer holds all N planes; a plan with g < N reads its group's planes at an offset,
+    and k beyond one int32-safe chunk adds the second chunk into the product planes."""
+    import torch
+    import gpu_util as gu
+    import immerdink_b200 as imd
+    rng = np.random.default_rng(k)
+    A = gu.dev_f64(rng.uniform(-1, 1, (m, k))).view(m, k)
+    B = gu.dev_f64(rng.uniform(-1, 1, (k, n))).view(k, n)
+    spec = "ik,kj->ij"
+    C0 = torch.zeros((m, n), dtype=torch.float64, device="cuda")
+    plan0 = imd.Plan(spec, A, B, C0, N=N, g=g)
+    w0 = torch.empty(plan0.workspace_bytes, dtype=torch.uint8, device="cuda")
+    plan0.contract(A, B, C0, workspace=w0)
+    for which in ((0,), (1,), (0, 1)):
+        pks, bufs = [None, None], [None, None]
+        for x in which:
+            pks[x] = imd.Pack(plan0.pack_spec(x))
+            bufs[x] = torch.empty(pks[x].pack_bytes, dtype=torch.uint8, device="cuda")
+            pks[x].pack((A, B)[x], bufs[x],
+                        workspace=torch.empty(pks[x].workspace_bytes, dtype=torch.uint8, device="cuda"))
+        plan = imd.Plan(spec, A, B, C0, N=N, g=g, packs=tuple(pks))
+        C1 = torch.full((m, n), -1.0, dtype=torch.float64, device="cuda")
+        plan.contract(A, B, C1, workspace=torch.empty(max(plan.workspace_bytes, 1), dtype=torch.uint8, device="cuda"),
+                      packed=tuple(bufs))
+        torch.cuda.synchronize()
+        assert gu.lib().lib.imd_test_device_error() == 0
+        assert same_bits(C1.cpu().numpy(), C0.cpu().numpy()), which
+    import imd_oracle as orc
+    want = orc.gemm(A.cpu().numpy(), B.cpu().numpy().T.copy(), N)
+    assert same_bits(C0.cpu().numpy(), want)
