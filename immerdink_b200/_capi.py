@@ -33,6 +33,10 @@ SIGNATURES = {
     "imd_pack": [_P, _P, _P, C.c_size_t, _P, C.c_size_t, _P],
     "imd_plan_create_packed": [_P, _T, _T, _T, _O, _P, _P, C.POINTER(C.c_void_p)],
     "imd_contract_builtin_ws": [_P, C.c_double, _P, _P, C.c_double, _P, _P],
+    "imd_contract_packed_part": [_P, C.c_double, C.POINTER(Operand), C.POINTER(Operand), C.c_double,
+                                 _P, _P, C.c_size_t, _P, C.c_int32],
+    "imd_pack_scatter": [_P, _P, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p), C.c_size_t, _P,
+                         C.c_size_t, _P],
     "imd_contract_packed": [_P, C.c_double, C.POINTER(Operand), C.POINTER(Operand), C.c_double,
                             _P, _P, C.c_size_t, _P],
 }

@@ -247,6 +247,43 @@ imd_status_t imd_pack(imd_pack_t pack, const double* X, void* packed, size_t pac
   }
 }
 
+/* Extension (no counterpart in the reference): imd_pack of a PIECE of a slab for all the slab's
+ * consumers at once. The pack handle describes the piece X (r rows per batch); its rows land as
+ * rows [row_offset, row_offset + r) of packed buffers whose batches have slab_rows rows, in the
+ * byte layout imd_pack_layout reports for that slab (same K, batches, N, rounding), and every one
+ * of the num_dest buffers (1..8, dest[0] the caller's own, the others possibly other GPUs' memory
+ * mapped into this process) receives the same bytes by plain stores. Gaps and tail are zeroed in
+ * dest[0] only. Checks: null pointers, ranges -> INVALID_VALUE; 256-byte alignment -> MISALIGNED;
+ * dest_bytes below the slab's pack_bytes, ws_bytes below the piece's pack_ws_bytes ->
+ * INSUFFICIENT_WORKSPACE. Enqueue only. */
+IMD_API imd_status_t imd_pack_scatter(imd_pack_t piece, const double* X, int64_t slab_rows,
+                                      int64_t row_offset, int32_t num_dest, void* const* dest,
+                                      size_t dest_bytes, void* ws, size_t ws_bytes,
+                                      cudaStream_t stream) {
+  if (piece == nullptr || dest == nullptr || num_dest < 1 || num_dest > 8 || row_offset < 0 ||
+      slab_rows < 0)
+    return IMD_STATUS_INVALID_VALUE;
+  const imd::PackLowered& pl = piece->pl;
+  if (pl.r > slab_rows || row_offset > slab_rows - pl.r) return IMD_STATUS_INVALID_VALUE;
+  imd::PackRegions slab;
+  if (!imd::pack_regions(pl.b, slab_rows, pl.k, pl.N, pl.k_align, &slab)) return IMD_STATUS_INVALID_VALUE;
+  const uint64_t need_ws = pl.ws_bytes;
+  if (pl.layout.total == 0) return IMD_STATUS_SUCCESS;  // an empty piece
+  if (X == nullptr || (need_ws > 0 && ws == nullptr)) return IMD_STATUS_INVALID_VALUE;
+  for (int32_t i = 0; i < num_dest; ++i)
+    if (dest[i] == nullptr) return IMD_STATUS_INVALID_VALUE;
+  if (!aligned(X, 8) || (need_ws > 0 && !aligned(ws, imd::kRegionAlign))) return IMD_STATUS_MISALIGNED;
+  for (int32_t i = 0; i < num_dest; ++i)
+    if (!aligned(dest[i], imd::kRegionAlign)) return IMD_STATUS_MISALIGNED;
+  if (dest_bytes < slab.total || ws_bytes < need_ws) return IMD_STATUS_INSUFFICIENT_WORKSPACE;
+  try {
+    return imd::enqueue_pack_scatter(piece->exec, piece->res, slab, slab_rows, row_offset, X, dest,
+                                     num_dest, ws, stream);
+  } catch (...) {
+    return IMD_STATUS_CUDA_ERROR;
+  }
+}
+
 imd_status_t imd_plan_create_packed(imd_handle_t handle, const imd_tensor_t* A,
                                     const imd_tensor_t* B, const imd_tensor_t* C,
                                     const imd_options_t* options, imd_pack_t packA,
@@ -255,9 +292,11 @@ imd_status_t imd_plan_create_packed(imd_handle_t handle, const imd_tensor_t* A,
   return plan_create(handle, A, B, C, options, packs, plan);
 }
 
-imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operand_t* A,
-                                 const imd_operand_t* B, double beta, double* C, void* ws,
-                                 size_t ws_bytes, cudaStream_t stream) {
+IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
+                                              const imd_operand_t* A, const imd_operand_t* B,
+                                              double beta, double* C, void* ws, size_t ws_bytes,
+                                              cudaStream_t stream, int32_t part) {
+  if (part < 0 || part > 2) return IMD_STATUS_INVALID_VALUE;
   // order: operands and packed slots; null pointers; empty output; ALIASING; MISALIGNED; sizes
   if (plan == nullptr || A == nullptr || B == nullptr) return IMD_STATUS_INVALID_VALUE;
   const imd::ExecPlan& e = plan->exec;
@@ -274,7 +313,9 @@ imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operan
   const bool reads_ab = alpha != 0.0 && e.k != 0;
   const bool reads_pack = reads_ab && e.emulated();
   const uint64_t need = e.layout.total;
-  if (C == nullptr || (reads_ab && (A->data == nullptr || B->data == nullptr)) ||
+  // a part is defined for the emulated GEMM only; part 1 never reads the FP64 operands
+  if (part != 0 && !reads_pack) return IMD_STATUS_INVALID_VALUE;
+  if (C == nullptr || (reads_ab && part != 1 && (A->data == nullptr || B->data == nullptr)) ||
       (need > 0 && ws == nullptr))
     return IMD_STATUS_INVALID_VALUE;
   for (int x = 0; x < 2; ++x)
@@ -305,10 +346,16 @@ imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operan
   for (int x = 0; x < 2; ++x)
     if (!plan->slot_key[x].empty()) packed[role[x]] = op[x]->packed;
   try {
-    return imd::enqueue_contract(*plan, alpha, gA, gB, beta, C, ws, stream, packed);
+    return imd::enqueue_contract(*plan, alpha, gA, gB, beta, C, ws, stream, packed, part);
   } catch (...) {
     return IMD_STATUS_CUDA_ERROR;
   }
+}
+
+imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operand_t* A,
+                                 const imd_operand_t* B, double beta, double* C, void* ws,
+                                 size_t ws_bytes, cudaStream_t stream) {
+  return imd_contract_packed_part(plan, alpha, A, B, beta, C, ws, ws_bytes, stream, 0);
 }
 
 /* ---- verification hooks (not part of the drop-in ABI) ---------------------------------------- */

@@ -47,12 +47,21 @@ imd_status_t gemm_reference_launch(const GemmShape& s, const int8_t* RA, const i
                                    uint8_t* W, cudaStream_t stream);
 
 // `packed[x]`: the packed buffer of the post-swap operand x of a plan with that slot packed.
+// `part`: 0 the whole call; 1 everything but the outputs of the native path (A and B are not
+// read); 2 only those outputs, from the shifts and flags already in the packs / workspace.
 imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
                               const double* B, double beta, double* C, void* ws,
-                              cudaStream_t stream, const void* const packed[2] = nullptr);
+                              cudaStream_t stream, const void* const packed[2] = nullptr,
+                              int part = 0);
 // imd_pack: shifts, flags and all N residue planes of X into `packed` (every byte written).
 imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const PackRegions& layout,
                           const double* X, void* packed, void* ws, cudaStream_t stream);
+// imd_pack_scatter: the rows of a piece into rows [row0, row0 + rows) of up to 8 packed buffers of
+// a slab with slab_rows rows per batch (layout = that slab's).
+imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables,
+                                  const PackRegions& layout, int64_t slab_rows, int64_t row0,
+                                  const double* X, void* const* dest, int n_dest, void* ws,
+                                  cudaStream_t stream);
 imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stream);
 
 // Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.

@@ -27,6 +27,7 @@ namespace {
 __device__ unsigned int g_error_word = 0;
 
 constexpr int kThreads = 256;
+constexpr int kMaxDests = 8;  // buffers one pack launch can write (the consumers of a slab)
 
 // ---- scatter vectors -------------------------------------------------------------------------
 struct VecParams {
@@ -95,8 +96,13 @@ struct ScaleParams {
   int32_t rows_fast;
   int32_t lhs_shift;
   Wide<8> rhs;
-  int16_t* sigma;
-  uint8_t* flag;
+  // Outputs: row i of batch lambda at index lambda * out_rows + out_row0 + i of every destination
+  // (one destination and out_rows = rows, out_row0 = 0 inside a contraction; several, possibly
+  // in other GPUs' memory, when a piece of a slab is packed for all its consumers).
+  int64_t out_rows, out_row0;
+  int32_t n_out;
+  int16_t* sigma[kMaxDests];
+  uint8_t* flag[kMaxDests];
 };
 
 __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ ScaleParams p) {
@@ -244,8 +250,12 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
       sg = dev::shift_from_sum(s_hi[slot], s_lo[slot], p.lhs_shift, p.rhs, gamma);
   }
   if (live && kl == 0) {
-    p.sigma[rho] = static_cast<int16_t>(sg);
-    p.flag[rho] = (gf >> 30) & 1;
+    const int64_t lam = rho / p.rows;
+    const int64_t at = lam * p.out_rows + p.out_row0 + (rho - lam * p.rows);
+    for (int dst = 0; dst < p.n_out; ++dst) {
+      p.sigma[dst][at] = static_cast<int16_t>(sg);
+      p.flag[dst][at] = (gf >> 30) & 1;
+    }
   }
 }
 
@@ -258,13 +268,18 @@ struct ResidueParams {
   const double* X;
   const int64_t *row, *kv, *bat;
   int64_t rows, rows_pad, batches, k, k_hat;
+  // Output rows: a batch's planes have plane_rows rows, the rows of this launch start at row0
+  // (plane_rows = rows_pad, row0 = 0 inside a contraction); sigma has sigma_rows rows per batch
+  // (rows inside a contraction, plane_rows in a packed buffer) and the same row0.
+  int64_t plane_rows, row0, sigma_rows;
   int64_t k_run;       // length of the runs of K positions that are adjacent in memory (0: none)
   int32_t rows_fast;
   int32_t lg_fast;     // log2 of the threads of a CTA that run along the fast direction
   int32_t trunc;
   int32_t mod0, mods;  // first modulus and number of moduli of the group
   const int16_t* sigma;
-  int8_t* R;
+  int32_t n_out;
+  int8_t* R[kMaxDests];
   ResidueTables t;
 };
 
@@ -280,7 +295,7 @@ __global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ R
   const int64_t fast_n = p.rows_fast ? total_rows : chunks;
   const int64_t slow_n = p.rows_fast ? chunks : total_rows;
   if (fast >= fast_n) return;
-  const int64_t plane = p.batches * p.rows_pad * p.k_hat;
+  const int64_t plane = p.batches * p.plane_rows * p.k_hat;
   for (int64_t slow = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
        slow < slow_n; slow += static_cast<int64_t>(gridDim.y) * per) {
     const int64_t rho = p.rows_fast ? fast : slow;
@@ -295,7 +310,7 @@ __global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ R
     const int64_t h0 = c << 4;
     if (live) {
       const double* base = p.X + p.bat[lam] + p.row[i];
-      const int sg = p.sigma[lam * p.rows + i];
+      const int sg = p.sigma[lam * p.sigma_rows + p.row0 + i];
       // all sixteen loads are issued before anything is computed
       uint64_t raw[16];
       bool run = false;
@@ -339,7 +354,7 @@ __global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ R
         }
       }
     }
-    int8_t* out = p.R + (lam * p.rows_pad + i) * p.k_hat + h0;
+    const int64_t out = (lam * p.plane_rows + p.row0 + i) * p.k_hat + h0;
     for (int s = 0; s < p.mods; ++s) {
       uint32_t pk[4] = {0, 0, 0, 0};
       if (live) {
@@ -350,7 +365,8 @@ __global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ R
 #pragma unroll
         for (int wd = 0; wd < 4; ++wd) pk[wd] = dev::symmetric4(p.t, l, pk[wd]);
       }
-      *reinterpret_cast<uint4*>(out + s * plane) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      for (int dst = 0; dst < p.n_out; ++dst)
+        *reinterpret_cast<uint4*>(p.R[dst] + out + s * plane) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
 }
@@ -365,6 +381,7 @@ struct CrtParams {
   Vectors v;
   int64_t m, n, n_hat, k, b;
   int32_t lg_fast;
+  int32_t part;  // 0 all outputs, 1 emulated outputs only, 2 native-path outputs only
   double alpha, beta;
   CrtTables t;
 };
@@ -419,22 +436,34 @@ __global__ void __launch_bounds__(kThreads, 3) k_crt(const __grid_constant__ Crt
       lam = rho / p.m;
       i = rho - lam * p.m;
     }
+    bool fa = p.fA[rho] != 0;
+    const int16_t* tau = p.tau + lam * p.n + j0;
+    const uint8_t* fb = p.fB + lam * p.n + j0;
+    bool f0 = fb[0] != 0, f1 = left > 1 && fb[1] != 0, f2 = left > 2 && fb[2] != 0,
+         f3 = left > 3 && fb[3] != 0;
+    // part 0: every output. part 1: only the outputs of the emulated path (A and B are not read);
+    // part 2: only the outputs of the native path (flagged row or column).
+    bool w0 = true, w1 = true, w2 = true, w3 = true;
+    if (p.part != 0) {
+      const bool native = p.part == 2;
+      if (native && !(fa || f0 || f1 || f2 || f3)) continue;
+      w0 = (fa || f0) == native, w1 = (fa || f1) == native, w2 = (fa || f2) == native,
+      w3 = (fa || f3) == native;
+      if (!native) fa = f0 = f1 = f2 = f3 = false;  // skipped outputs: keep off the native path
+    }
     const uint8_t* w = p.W + rho * p.n_hat + j0;
     uint32_t packed[N];
 #pragma unroll
     for (int l = 0; l < N; ++l) packed[l] = *reinterpret_cast<const uint32_t*>(w + l * plane);
     const int si = p.sigma[rho];
-    const bool fa = p.fA[rho] != 0;
-    const int16_t* tau = p.tau + lam * p.n + j0;
-    const uint8_t* fb = p.fB + lam * p.n + j0;
     double D0, D1 = 0.0, D2 = 0.0, D3 = 0.0;
-    D0 = crt_value<N, 0>(p, packed, lam, i, j0, si, fa, tau[0], fb[0] != 0);
-    if (left > 1) D1 = crt_value<N, 1>(p, packed, lam, i, j0 + 1, si, fa, tau[1], fb[1] != 0);
-    if (left > 2) D2 = crt_value<N, 2>(p, packed, lam, i, j0 + 2, si, fa, tau[2], fb[2] != 0);
-    if (left > 3) D3 = crt_value<N, 3>(p, packed, lam, i, j0 + 3, si, fa, tau[3], fb[3] != 0);
+    D0 = crt_value<N, 0>(p, packed, lam, i, j0, si, fa, tau[0], f0);
+    if (left > 1) D1 = crt_value<N, 1>(p, packed, lam, i, j0 + 1, si, fa, tau[1], f1);
+    if (left > 2) D2 = crt_value<N, 2>(p, packed, lam, i, j0 + 2, si, fa, tau[2], f2);
+    if (left > 3) D3 = crt_value<N, 3>(p, packed, lam, i, j0 + 3, si, fa, tau[3], f3);
     double* crow = p.C + p.v.c_bat[lam] + p.v.c_row[i];
     double* c = crow + c0;
-    if (adjacent && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+    if (adjacent && w0 && w1 && w2 && w3 && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
       double2* cv = reinterpret_cast<double2*>(c);
       double2 lo = make_double2(0.0, 0.0), hi = lo;
       if (p.beta != 0.0) {
@@ -448,10 +477,10 @@ __global__ void __launch_bounds__(kThreads, 3) k_crt(const __grid_constant__ Crt
       cv[0] = lo;
       cv[1] = hi;
     } else {
-      *c = finish(D0, p.alpha, p.beta, c);
-      if (left > 1) crow[c1] = finish(D1, p.alpha, p.beta, crow + c1);
-      if (left > 2) crow[c2] = finish(D2, p.alpha, p.beta, crow + c2);
-      if (left > 3) crow[c3] = finish(D3, p.alpha, p.beta, crow + c3);
+      if (w0) *c = finish(D0, p.alpha, p.beta, c);
+      if (left > 1 && w1) crow[c1] = finish(D1, p.alpha, p.beta, crow + c1);
+      if (left > 2 && w2) crow[c2] = finish(D2, p.alpha, p.beta, crow + c2);
+      if (left > 3 && w3) crow[c3] = finish(D3, p.alpha, p.beta, crow + c3);
     }
   }
 }
@@ -649,6 +678,16 @@ struct OperandView {
   int64_t rows, rows_pad;  // rows per batch; rows per batch of the residue planes
   bool rows_fast;
   int64_t k_run;
+  // Where the rows land in the outputs (see ScaleParams / ResidueParams); 0 = the defaults.
+  int64_t out_rows = 0, out_row0 = 0;
+};
+
+// Destinations of a scale / residue launch.
+struct PackDests {
+  int n = 1;
+  int16_t* sigma[kMaxDests] = {};
+  uint8_t* flag[kMaxDests] = {};
+  int8_t* res[kMaxDests] = {};
 };
 
 OperandView operand_view(const ExecPlan& e, const Vectors& v, int x, const double* X) {
@@ -666,8 +705,7 @@ OperandView operand_view(const ExecPlan& e, const Vectors& v, int x, const doubl
   return o;
 }
 
-bool launch_scale(const ExecPlan& e, const OperandView& o, int16_t* sigma, uint8_t* flag,
-                  cudaStream_t stream) {
+bool launch_scale(const ExecPlan& e, const OperandView& o, const PackDests& d, cudaStream_t stream) {
   ScaleParams p{};
   p.X = o.X;
   p.row = o.row, p.kv = o.kv, p.bat = o.bat;
@@ -678,8 +716,10 @@ bool launch_scale(const ExecPlan& e, const OperandView& o, int16_t* sigma, uint8
   p.lg_rt = scale_lg_rt(o.rows_fast, e.k, o.rows * e.b);
   p.lhs_shift = e.lhs_shift;
   p.rhs = e.rhs;
-  p.sigma = sigma;
-  p.flag = flag;
+  p.out_rows = o.out_rows > 0 ? o.out_rows : o.rows;
+  p.out_row0 = o.out_row0;
+  p.n_out = d.n;
+  for (int i = 0; i < d.n; ++i) p.sigma[i] = d.sigma[i], p.flag[i] = d.flag[i];
   const int64_t rt = int64_t{1} << p.lg_rt;
   const int64_t blocks = (p.rows * p.batches + rt - 1) / rt;
   k_scale<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(p);
@@ -688,7 +728,7 @@ bool launch_scale(const ExecPlan& e, const OperandView& o, int16_t* sigma, uint8
 
 // Residue planes of moduli [mod0, mod0 + mods) of one operand into R[slot][batch][rows_pad][k_hat].
 bool launch_residues(const ExecPlan& e, const ResidueTables& t, const OperandView& o,
-                     const int16_t* sigma, int8_t* R, int mod0, int mods, cudaStream_t stream) {
+                     const PackDests& d, int mod0, int mods, cudaStream_t stream) {
   ResidueParams p{};
   p.X = o.X;
   p.row = o.row, p.kv = o.kv, p.bat = o.bat;
@@ -702,8 +742,13 @@ bool launch_residues(const ExecPlan& e, const ResidueTables& t, const OperandVie
   p.trunc = e.trunc;
   p.mod0 = mod0;
   p.mods = mods;
-  p.sigma = sigma;
-  p.R = R;
+  const bool placed = o.out_rows > 0;  // rows of a larger packed buffer
+  p.plane_rows = placed ? o.out_rows : o.rows_pad;
+  p.sigma_rows = placed ? o.out_rows : o.rows;
+  p.row0 = o.out_row0;
+  p.sigma = d.sigma[0];
+  p.n_out = d.n;
+  for (int i = 0; i < d.n; ++i) p.R[i] = d.res[i];
   p.t = t;
   const int64_t fast_n = p.rows_fast ? p.rows_pad * p.batches : (p.k_hat >> 4);
   const int64_t slow_n = p.rows_fast ? (p.k_hat >> 4) : p.rows_pad * p.batches;
@@ -722,7 +767,7 @@ bool launch_residues(const ExecPlan& e, const ResidueTables& t, const OperandVie
 
 imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const double* A,
                               const double* B, double beta, double* C, void* ws,
-                              cudaStream_t stream, const void* const packed[2]) {
+                              cudaStream_t stream, const void* const packed[2], int part) {
   const ExecPlan& e = plan.exec;
   char* base = static_cast<char*>(ws);
   auto region = [&](int r) { return base + e.layout.offset[r]; };
@@ -770,17 +815,22 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   uint8_t* W = reinterpret_cast<uint8_t*>(region(IMD_REGION_W));
   const OperandView ov[2] = {operand_view(e, v, 0, A), operand_view(e, v, 1, B)};
 
-  for (int x = 0; x < 2; ++x)
-    if (!from_pack[x] &&
-        !launch_scale(e, ov[x], const_cast<int16_t*>(sX[x]), const_cast<uint8_t*>(fX[x]), stream))
+  PackDests dest[2];
+  const bool emulate = part != 2;  // part 2: only the native-path outputs, from the flags at hand
+  for (int x = 0; x < 2; ++x) {
+    dest[x].sigma[0] = const_cast<int16_t*>(sX[x]);
+    dest[x].flag[0] = const_cast<uint8_t*>(fX[x]);
+    dest[x].res[0] = const_cast<int8_t*>(RX[x]);
+    if (emulate && !from_pack[x] && !launch_scale(e, ov[x], dest[x], stream))
       return IMD_STATUS_CUDA_ERROR;
+  }
 
   mark(1, stream);
   GemmPlanInfo info;
   info.encode_tiled = plan.encode_tiled;
   info.error_word = static_cast<unsigned int*>(plan.error_word);
   info.sms = plan.sms;
-  for (int g0 = 0; g0 < e.N; g0 += e.g) {
+  for (int g0 = 0; emulate && g0 < e.N; g0 += e.g) {
     const int mods = e.N - g0 < e.g ? e.N - g0 : e.g;
     const int8_t* Rg[2];
     for (int x = 0; x < 2; ++x) {
@@ -789,7 +839,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
         continue;
       }
       Rg[x] = RX[x];
-      if (!launch_residues(e, plan.res, ov[x], sX[x], const_cast<int8_t*>(RX[x]), g0, mods, stream))
+      if (!launch_residues(e, plan.res, ov[x], dest[x], g0, mods, stream))
         return IMD_STATUS_CUDA_ERROR;
     }
     mark(2, stream);
@@ -810,6 +860,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   p.v = v;
   p.m = e.m, p.n = e.n, p.n_hat = e.n_hat, p.k = e.k, p.b = e.b;
   p.alpha = alpha, p.beta = beta;
+  p.part = part;
   p.t = plan.crt;
   const int64_t quads = e.n_hat >> 2, rows_total = e.b * e.m;
   p.lg_fast = 0;
@@ -853,8 +904,20 @@ __global__ void __launch_bounds__(kThreads) k_zero_ranges(const __grid_constant_
 
 imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const PackRegions& layout,
                           const double* X, void* packed, void* ws, cudaStream_t stream) {
-  if (layout.total == 0) return IMD_STATUS_SUCCESS;
-  uint8_t* out = static_cast<uint8_t*>(packed);
+  void* const one[1] = {packed};
+  return enqueue_pack_scatter(e, tables, layout, e.m, 0, X, one, 1, ws, stream);
+}
+
+// The rows of X (a piece) as rows [row0, row0 + e.m) of packed buffers whose batches have
+// slab_rows rows and the byte layout `layout`; every destination gets the same bytes (they may be
+// other GPUs' memory: plain stores). Gaps and tail are zeroed in dest[0], the caller's own buffer.
+imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables,
+                                  const PackRegions& layout, int64_t slab_rows, int64_t row0,
+                                  const double* X, void* const* dest, int n_dest, void* ws,
+                                  cudaStream_t stream) {
+  if (layout.total == 0 || e.m == 0) return IMD_STATUS_SUCCESS;
+  if (n_dest < 1 || n_dest > kMaxDests) return IMD_STATUS_INVALID_VALUE;
+  uint8_t* out = static_cast<uint8_t*>(dest[0]);
   int64_t* vec = static_cast<int64_t*>(ws);
   mark(0, stream);
   VecParams vp;
@@ -864,7 +927,7 @@ imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const 
   k_vectors<<<grid_for(e.vec_count, 1 << 20), kThreads, 0, stream>>>(vp, vec);
   if (!launched()) return IMD_STATUS_CUDA_ERROR;
 
-  const uint64_t planes = static_cast<uint64_t>(e.N) * e.b * e.m * e.k_hat;
+  const uint64_t planes = static_cast<uint64_t>(e.N) * e.b * slab_rows * e.k_hat;
   ZeroRanges z{};
   uint64_t longest = 0;
   for (int r = 0; r < 3; ++r) {
@@ -888,11 +951,17 @@ imd_status_t enqueue_pack(const ExecPlan& e, const ResidueTables& tables, const 
   o.k_run = e.modes.count[kClsK] > 0 && e.modes.stride[e.modes.first[kClsK]][kTenA] == 1
                 ? e.modes.extent[e.modes.first[kClsK]]
                 : 0;
-  int16_t* sigma = reinterpret_cast<int16_t*>(out + layout.offset[0]);
-  if (!launch_scale(e, o, sigma, out + layout.offset[1], stream)) return IMD_STATUS_CUDA_ERROR;
-  if (!launch_residues(e, tables, o, sigma, reinterpret_cast<int8_t*>(out + layout.offset[2]), 0,
-                       e.N, stream))
-    return IMD_STATUS_CUDA_ERROR;
+  o.out_rows = slab_rows, o.out_row0 = row0;
+  PackDests d;
+  d.n = n_dest;
+  for (int i = 0; i < n_dest; ++i) {
+    uint8_t* base = static_cast<uint8_t*>(dest[i]);
+    d.sigma[i] = reinterpret_cast<int16_t*>(base + layout.offset[0]);
+    d.flag[i] = base + layout.offset[1];
+    d.res[i] = reinterpret_cast<int8_t*>(base + layout.offset[2]);
+  }
+  if (!launch_scale(e, o, d, stream)) return IMD_STATUS_CUDA_ERROR;
+  if (!launch_residues(e, tables, o, d, 0, e.N, stream)) return IMD_STATUS_CUDA_ERROR;
   mark(6, stream);
   return IMD_STATUS_SUCCESS;
 }

@@ -259,6 +259,18 @@ class Pack:
                                          f"{self.workspace_bytes} bytes needed; given {no}, {nw})")
         return out
 
+    def scatter_ptr(self, X, slab_rows, row_offset, dests, dest_bytes, ws, ws_bytes, stream=0):
+        """imd_pack_scatter with raw integers: this pack describes a PIECE of a slab; its rows go to
+        rows [row_offset, row_offset + r) of every packed buffer in `dests` (pointers; dests[0] the
+        caller's own), each laid out for a slab of `slab_rows` rows per batch."""
+        if self.closed:
+            raise ValueError(f"{self!r} is closed")
+        arr = (ct.c_void_p * len(dests))(*[int(d) for d in dests])
+        st = self.lib.lib.imd_pack_scatter(self._h, X, int(slab_rows), int(row_offset), len(dests), arr,
+                                           int(dest_bytes), ws, int(ws_bytes), stream)
+        if st:
+            raise _error(st, "imd_pack_scatter")
+
     def pack_ptr(self, X, packed, packed_bytes, ws, ws_bytes, stream=0):
         """imd_pack with raw integers: only the C checks, no PackedBuffer record."""
         if self.closed:
@@ -456,10 +468,12 @@ class Plan:
     def host_bytes(self):
         return self.lowering["plan_host_bytes"]
 
-    def contract(self, A, B, C, *, alpha=1.0, beta=0.0, workspace=None, stream=None, packed=None):
+    def contract(self, A, B, C, *, alpha=1.0, beta=0.0, workspace=None, stream=None, packed=None,
+                 part=0):
         """C <- alpha A.B + beta C on `stream`. Arrays must have the plan's shapes and strides;
         workspace >= workspace_bytes, 256-byte aligned, one in-flight call per workspace.
-        Returns C."""
+        part (packed plans, an extension): 0 the whole call; 1 all outputs but those of the native
+        path (A and B are not read); 2 only those (imd_contract_packed_part). Returns C."""
         if self._h is None:
             raise ValueError("plan is closed")
         s = 0 if stream is None else stream_handle(stream)
@@ -470,10 +484,17 @@ class Plan:
         pw, nw = (None, 0) if workspace is None else _arrays.buffer(workspace, "workspace",
                                                                     stream=s, device=dev)
         if self._packed:
-            st = self._fn(self._h, alpha, *self._operands(pa, pb, packed, s), beta, pc, pw, nw, s)
+            ops = self._operands(pa, pb, packed, s)
+            if part:
+                st = self.lib.lib.imd_contract_packed_part(self._h, alpha, *ops, beta, pc, pw, nw, s,
+                                                           int(part))
+            else:
+                st = self._fn(self._h, alpha, *ops, beta, pc, pw, nw, s)
         else:
             if packed is not None and any(x is not None for x in packed):
                 raise ValueError("packed buffers given to a plan without packs")
+            if part:
+                raise ValueError("parts are defined for plans with packs")
             st = self._fn(self._h, alpha, pa, pb, beta, pc, pw, nw, s)
         if st:
             raise self._fail(st, nw)

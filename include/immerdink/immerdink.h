@@ -99,6 +99,36 @@ IMD_API imd_status_t imd_contract_builtin_ws(imd_plan_t plan, double alpha, cons
                                              const double* B, double beta, double* C,
                                              cudaStream_t stream);
 
+/* imd_pack of a PIECE of a slab for all consumers of the slab at once (no counterpart in the
+ * reference; used by the multi-GPU driver, where the other destinations are peers' buffers mapped
+ * into this process). The pack handle describes the piece X (r rows per batch); its rows land as
+ * rows [row_offset, row_offset + r) of packed buffers whose batches have slab_rows rows, laid out
+ * as imd_pack_layout describes that slab (same K, batches, N, rounding); every one of the
+ * num_dest buffers (1..8) receives the same bytes by plain stores. dest[0] is the caller's own
+ * buffer: its alignment gaps and tail are zeroed here. Checks: NULL pointers and ranges ->
+ * INVALID_VALUE; an empty piece -> SUCCESS; X 8-byte, dest[] and ws 256-byte aligned -> else
+ * MISALIGNED; dest_bytes below the slab's pack_bytes or ws_bytes below the piece's pack_ws_bytes
+ * -> INSUFFICIENT_WORKSPACE. Enqueue only: no allocation, no synchronisation. */
+IMD_API imd_status_t imd_pack_scatter(imd_pack_t piece, const double* X, int64_t slab_rows,
+                                      int64_t row_offset, int32_t num_dest, void* const* dest,
+                                      size_t dest_bytes, void* ws, size_t ws_bytes,
+                                      cudaStream_t stream);
+
+/* imd_contract_packed in two parts (no counterpart in the reference; used by the multi-GPU driver
+ * to start the emulated GEMM before the FP64 operands of other GPUs have arrived). part 0: the
+ * whole call. part 1: everything except the outputs of the native path (outputs whose row of A or
+ * column of B holds a non-finite entry): those elements of C are left untouched and A->data,
+ * B->data are not read (they may be NULL). part 2: only those outputs, by the native path, from
+ * the shifts and flags already in the packed buffers (for an in-line operand: in the workspace,
+ * as part 1 of the same call left them); no GEMM runs. Parts 1 and 2 together, in this order and
+ * with the same arguments, write exactly what part 0 writes. Same checks as
+ * imd_contract_packed; part outside 0..2, or a part other than 0 on a plan whose call would not
+ * run the emulated GEMM -> INVALID_VALUE. */
+IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
+                                              const imd_operand_t* A, const imd_operand_t* B,
+                                              double beta, double* C, void* ws, size_t ws_bytes,
+                                              cudaStream_t stream, int32_t part);
+
 #ifdef __cplusplus
 }
 #endif

@@ -294,3 +294,86 @@ def test_packed_with_residue_groups_and_k_chunks(m, n, k, N, g):
     import imd_oracle as orc
     want = orc.gemm(A.cpu().numpy(), B.cpu().numpy().T.copy(), N)
     assert same_bits(C0.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("b,rows,k,N,pieces", [(1, 96, 200, 14, 3), (2, 40, 97, 9, 2), (1, 1000, 64, 18, 4)])
+def test_pack_scatter_assembles_a_slab_from_pieces(b, rows, k, N, pieces):
+    """Pieces of a slab packed one by one (each into two destinations) give exactly the bytes of
+    imd_pack of the whole slab."""
+    import torch
+    import gpu_util as gu
+    import immerdink_b200 as imd
+    from immerdink_b200 import host
+    rng = np.random.default_rng(rows)
+    X = rng.standard_normal((b, rows, k)) * np.exp2(rng.integers(-30, 30, (b, rows, 1)))
+    X[0, 3, 5] = np.nan
+    dX = gu.dev_f64(X).view(b, rows, k)
+    lab = tuple(ord(c) for c in "bik")
+    whole = host.PackSpec(host.Desc((b, rows, k), (rows * k, k, 1), lab), (ord("k"),), (ord("b"),),
+                          (ord("i"),), N, "RN", "GIVEN")
+    pk = imd.Pack(whole)
+    want, _ = pack_on_device_np(pk, dX)
+    rp = rows // pieces
+    piece = imd.Pack(host.PackSpec(host.Desc((b, rp, k), (rows * k, k, 1), lab), (ord("k"),), (ord("b"),),
+                                   (ord("i"),), N, "RN", "GIVEN"))
+    bufs = [gu.Workspace(pk.pack_bytes) for _ in range(2)]
+    ws = gu.Workspace(piece.workspace_bytes)
+    for x in range(pieces):
+        order = (0, 1) if x % 2 == 0 else (1, 0)     # either buffer may be "the caller's own"
+        piece.scatter_ptr(dX.data_ptr() + 8 * x * rp * k, rows, x * rp, [bufs[o].ptr for o in order],
+                          pk.pack_bytes, ws.ptr, piece.workspace_bytes)
+    torch.cuda.synchronize()
+    for buf in bufs:
+        assert buf.guards_intact()
+        assert np.array_equal(buf.region(0, pk.pack_bytes, np.uint8), want)
+    with pytest.raises(imd.InvalidValueError):
+        piece.scatter_ptr(dX.data_ptr(), rows, rows - rp + 1, [bufs[0].ptr], pk.pack_bytes, ws.ptr,
+                          piece.workspace_bytes)
+    with pytest.raises(imd.InsufficientWorkspaceError):
+        piece.scatter_ptr(dX.data_ptr(), rows, 0, [bufs[0].ptr], pk.pack_bytes - 1, ws.ptr,
+                          piece.workspace_bytes)
+
+
+def pack_on_device_np(pk, X_dev):
+    buf, got = pack_on_device(pk, X_dev, 0)
+    return got.copy(), buf
+
+
+def test_contract_packed_in_two_parts():
+    """Part 1 (emulated outputs, FP64 operands not read) then part 2 (native-path outputs) write
+    exactly what the whole call writes; part 1 alone leaves the flagged outputs untouched."""
+    import torch
+    import gpu_util as gu
+    import immerdink_b200 as imd
+    m, n, k, N = 70, 45, 130, 10
+    rng = np.random.default_rng(8)
+    A, B = rng.standard_normal((m, k)), rng.standard_normal((k, n))
+    A[3, 7] = np.inf
+    A[50, 0] = np.nan
+    B[9, 44] = -np.inf
+    dA, dB = gu.dev_f64(A).view(m, k), gu.dev_f64(B).view(k, n)
+    spec = "ik,kj->ij"
+    C0 = torch.full((m, n), 0.5, dtype=torch.float64, device="cuda")
+    plan0 = imd.Plan(spec, dA, dB, C0, N=N)
+    pks = [imd.Pack(plan0.pack_spec(x)) for x in (0, 1)]
+    bufs = []
+    for x, pk in enumerate(pks):
+        bufs.append(torch.empty(pk.pack_bytes, dtype=torch.uint8, device="cuda"))
+        pk.pack((dA, dB)[x], bufs[x], workspace=torch.empty(pk.workspace_bytes, dtype=torch.uint8, device="cuda"))
+    plan = imd.Plan(spec, dA, dB, C0, N=N, packs=tuple(pks))
+    ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+    plan.contract(dA, dB, C0, alpha=1.5, beta=2.0, workspace=ws, packed=tuple(bufs))
+    C1 = torch.full((m, n), 0.5, dtype=torch.float64, device="cuda")
+    junk = torch.full_like(dA, 123.0), torch.full_like(dB, -7.0)       # part 1 must not read these
+    plan.contract(junk[0], junk[1], C1, alpha=1.5, beta=2.0, workspace=ws, packed=tuple(bufs), part=1)
+    torch.cuda.synchronize()
+    got = C1.cpu().numpy()
+    flagged = np.zeros((m, n), bool)
+    flagged[[3, 50], :] = True
+    flagged[:, 44] = True
+    assert (got[flagged] == 0.5).all() and same_bits(got[~flagged], C0.cpu().numpy()[~flagged])
+    plan.contract(dA, dB, C1, alpha=1.5, beta=2.0, workspace=ws, packed=tuple(bufs), part=2)
+    torch.cuda.synchronize()
+    assert same_bits(C1.cpu().numpy(), C0.cpu().numpy())
+    with pytest.raises(imd.InvalidValueError):
+        plan.contract(dA, dB, C1, workspace=ws, packed=tuple(bufs), part=3)
