@@ -258,7 +258,8 @@ def run_ours(args, rank, world, local_rank):
         shard_a = synth(0, part.shard_shape(0), part.shard_start(0))
         shard_b = synth(1, part.shard_shape(1), part.shard_start(1))
         groups = idist.make_groups(world, dist)
-        rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups)
+        rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
+                                      exchange=args.exchange)
         A, B, plan, run_spec = rankc.A, rankc.B, rankc.plan, rankc.spec
         Cd = torch.empty(rankc.tile_shape, dtype=torch.float64, device=dev)
 
@@ -415,9 +416,15 @@ def run_ours(args, rank, world, local_rank):
                 dtype="int8xint8->int32 (FP64 emulation)", data="synthetic",
                 config=dict(workload=f"{args.workload}: {prob.spec} {prob.ext} N={prob.N} g={prob.g} "
                                      "alpha=1 beta=0, uniform[-1,1)",
-                            partition=(f"C modes (a,b) over {GRID[world]} ranks" + ("" if world == 1 else
-                                       "; every step all-gathers the slabs over NCCL (side stream), packs A "
-                                       "while B arrives and contracts the rank's tile")),
+                            partition=(f"C modes (a,b) over {GRID[world]} ranks" + (
+                                "" if world == 1 else
+                                "; every step each rank packs its own pieces of A and B once (imd_pack_scatter), "
+                                "copy engines push the residue planes into the other consumers' slab buffers "
+                                "over NVLink group by group while the GEMM of the previous group runs, and the "
+                                "tile is contracted from the packed slabs; FP64 pieces follow for the native "
+                                "path" if rankc.exchange == "residues" else
+                                "; every step all-gathers the FP64 slabs over NCCL (side stream), packs A "
+                                "while B arrives and contracts the rank's tile")),
                             exchange_alone_ms=exchange_ms, contraction_slabs_resident_ms=resident_ms,
                             l2="256 MB buffer written between timed steps",
                             gemm_view=[low["m"], low["n"], low["k"], low["b"]]),
@@ -425,8 +432,11 @@ def run_ours(args, rank, world, local_rank):
                          h2d_bytes_per_step=(srcA.numel() + srcB.numel()) * 8 * world,
                          d2h_bytes_per_step=Cd.numel() * 8 * world, ms_per_step=e2e_ms,
                          how=e2e_how, serial_ms=serial_ms, equals_device_result=e2e_exact),
-                # per step: the plan's launches (+ the 4 of imd_pack when A goes through a pack)
-                gpu_launches=(int(low["kernel_launches"]) + (4 if rankc is not None else 0)) * args.steps * world,
+                # per step: the plan's launches, + the 4 of imd_pack (FP64 exchange: A goes through a
+                # pack) or + 2 x 4 of imd_pack_scatter + the vector launches of the extra parts and
+                # the native-path CRT launch (residue exchange)
+                gpu_launches=(int(low["kernel_launches"]) +
+                              (0 if rankc is None else 4 if rankc.exchange == "fp64" else 12)) * args.steps * world,
                 clocks=clocks,
                 phases_ms=phase_ms,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peak_tops, unit="TOP/s (int8)",
@@ -477,6 +487,8 @@ def main():
     ap.add_argument("--workload", default="cc8000", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and DGEMM legs")
     ap.add_argument("--slabs", type=int, default=8, help="slabs of the host-operand pipeline (e2e)")
+    ap.add_argument("--exchange", default=None, choices=["residues", "fp64"],
+                    help="multi-GPU exchange (default: residues)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

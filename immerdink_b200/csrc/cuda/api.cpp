@@ -296,7 +296,7 @@ IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
                                               const imd_operand_t* A, const imd_operand_t* B,
                                               double beta, double* C, void* ws, size_t ws_bytes,
                                               cudaStream_t stream, int32_t part) {
-  if (part < 0 || part > 2) return IMD_STATUS_INVALID_VALUE;
+  if (part < 0 || (part > 3 && part < 16) || part >= 16 + imd::kMaxModuli) return IMD_STATUS_INVALID_VALUE;
   // order: operands and packed slots; null pointers; empty output; ALIASING; MISALIGNED; sizes
   if (plan == nullptr || A == nullptr || B == nullptr) return IMD_STATUS_INVALID_VALUE;
   const imd::ExecPlan& e = plan->exec;
@@ -315,7 +315,8 @@ IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
   const uint64_t need = e.layout.total;
   // a part is defined for the emulated GEMM only; part 1 never reads the FP64 operands
   if (part != 0 && !reads_pack) return IMD_STATUS_INVALID_VALUE;
-  if (C == nullptr || (reads_ab && part != 1 && (A->data == nullptr || B->data == nullptr)) ||
+  const bool native = part == 0 || part == 2;  // the parts that read the FP64 operands
+  if (C == nullptr || (reads_ab && native && (A->data == nullptr || B->data == nullptr)) ||
       (need > 0 && ws == nullptr))
     return IMD_STATUS_INVALID_VALUE;
   for (int x = 0; x < 2; ++x)

@@ -816,12 +816,20 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   const OperandView ov[2] = {operand_view(e, v, 0, A), operand_view(e, v, 1, B)};
 
   PackDests dest[2];
-  const bool emulate = part != 2;  // part 2: only the native-path outputs, from the flags at hand
+  // Parts (imd_contract_packed_part): 0 everything; 1 everything but the native-path outputs;
+  // 2 only those; 3 the CRT of the emulated outputs alone; 16 + i the GEMM of residue group i alone
+  // (with the shifts of in-line operands when i = 0 and their residues of that group).
+  const int only_group = part >= 16 ? part - 16 : -1;
+  const bool run_groups = part == 0 || part == 1 || only_group >= 0;
+  const bool run_scale = part == 0 || part == 1 || only_group == 0;
+  const bool run_crt = only_group < 0;
+  const int crt_part = part == 3 ? 1 : part;
+  if (only_group >= 0 && static_cast<int64_t>(only_group) * e.g >= e.N) return IMD_STATUS_INVALID_VALUE;
   for (int x = 0; x < 2; ++x) {
     dest[x].sigma[0] = const_cast<int16_t*>(sX[x]);
     dest[x].flag[0] = const_cast<uint8_t*>(fX[x]);
     dest[x].res[0] = const_cast<int8_t*>(RX[x]);
-    if (emulate && !from_pack[x] && !launch_scale(e, ov[x], dest[x], stream))
+    if (run_scale && !from_pack[x] && !launch_scale(e, ov[x], dest[x], stream))
       return IMD_STATUS_CUDA_ERROR;
   }
 
@@ -830,7 +838,8 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   info.encode_tiled = plan.encode_tiled;
   info.error_word = static_cast<unsigned int*>(plan.error_word);
   info.sms = plan.sms;
-  for (int g0 = 0; emulate && g0 < e.N; g0 += e.g) {
+  for (int g0 = 0; run_groups && g0 < e.N; g0 += e.g) {
+    if (only_group >= 0 && g0 != only_group * e.g) continue;
     const int mods = e.N - g0 < e.g ? e.N - g0 : e.g;
     const int8_t* Rg[2];
     for (int x = 0; x < 2; ++x) {
@@ -853,6 +862,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     mark(3, stream);
   }
 
+  if (!run_crt) return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
   CrtParams p{};
   p.W = W;
   p.sigma = sX[0], p.tau = sX[1], p.fA = fX[0], p.fB = fX[1];
@@ -860,7 +870,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   p.v = v;
   p.m = e.m, p.n = e.n, p.n_hat = e.n_hat, p.k = e.k, p.b = e.b;
   p.alpha = alpha, p.beta = beta;
-  p.part = part;
+  p.part = crt_part;
   p.t = plan.crt;
   const int64_t quads = e.n_hat >> 2, rows_total = e.b * e.m;
   p.lg_fast = 0;

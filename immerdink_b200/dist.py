@@ -10,13 +10,12 @@ single-GPU call.
 Ownership before the call: A is cut in `world` equal pieces along its label `lb` (a label of A and
 C), B likewise along `la`; the pieces of a slab belong to exactly the ranks that consume it.
 `gather` brings them together with one NCCL all-gather per operand inside the rank's grid column
-(A) or row (B); `RankContraction` is the whole step of one rank: both gathers on a side stream,
-operand A packed (`imd_pack`) as soon as its slab is complete and while B's slab is still arriving,
-then `imd_contract_packed`. The pieces land
+(A) or row (B); `RankContraction` is the whole step of one rank (exchange + compute). The pieces land
 side by side in one buffer [pieces, ...piece shape]; instead of copying them into a dense slab the
 plan describes that buffer directly by splitting the label in two (piece index, index inside the
 piece), which the strided-tensor front end handles at no cost.
 """
+import math
 from dataclasses import dataclass
 
 GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
@@ -133,35 +132,151 @@ def gather(part, shard_a, shard_b, out_a, out_b, groups, dist):
 
 
 class RankContraction:
-    """One rank's step of the partitioned contraction: exchange + compute, overlapped.
+    """One rank's step of the partitioned contraction: exchange + compute, overlapped. Two ways to
+    exchange (`exchange`):
 
-        side stream   all-gather A | all-gather B
-        main stream                | imd_pack(A) ........ | imd_contract_packed(A packed, B in line)
+    "residues" (the default with more than one rank): every rank quantises only ITS pieces of A
+    and B, once, for all N moduli, and the pack kernels store the shifts, flags and int8 residue
+    planes into its own packed slab buffers (`imd_pack_scatter`: the rows of a piece at their place
+    in the slab); copy engines then push those rows into the packed slab buffers of the other
+    consumers of the slab (peers' memory mapped through CUDA IPC, pitched peer-to-peer copies on a
+    side stream: no SM is taken from the persistent GEMM), residue group by residue group, so the
+    GEMM of one group runs while the planes of the next travel. No rank repeats another's
+    quantisation. The FP64 pieces, which only the native path of non-finite rows reads, travel last:
 
-    Owns the gathered buffers, the packed buffer and the workspaces (allocated here, once).
-    `dist` is torch.distributed (initialised) and `groups` = make_groups(world, dist); with
-    world = 1 the gathers are plain copies. Device memory and streams come from torch."""
+        main   barrier | pack own pieces | barrier, GEMM group 0 | barrier, GEMM group 1 | CRT | barrier, native path
+        side                             | push group 0 | push group 1 ...... | push FP64 pieces |
 
-    def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None):
+    "fp64": the slabs are all-gathered as FP64 (NCCL, side stream), A is packed as soon as its
+    slab is complete and while B's is still arriving, B is quantised in line.
+
+    Owns its buffers (allocated here, once). `dist` is torch.distributed (initialised) and
+    `groups` = make_groups(world, dist); with world = 1 nothing is exchanged. Device memory and
+    streams come from torch; the buffers peers write into are cudaMalloc allocations opened by
+    the peers through CUDA IPC (cuda-python)."""
+
+    def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
+                 exchange=None):
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
         self.groups = groups if groups is not None else ({part.rb: None}, {part.ra: None})
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.A = torch.empty(part.gathered_shape(0), dtype=torch.float64, device=dev)
-        self.B = torch.empty(part.gathered_shape(1), dtype=torch.float64, device=dev)
-        self.spec, _, _, lc = part.plan_layouts()
+        self.device = dev
+        self.spec, la_, lb_, lc = part.plan_layouts()
         self.tile_shape = lc.shape
-        proto = torch.empty(lc.shape, dtype=torch.float64, device=dev)
-        self.pack = _dev.Pack(_dev.pack_spec(self.spec, self.A, self.B, proto, operand=0, N=N, g=g,
-                                             rounding=rounding, lib=lib), lib=lib)
-        self.plan = _dev.Plan(self.spec, self.A, self.B, proto, N=N, g=g, rounding=rounding,
-                              packs=(self.pack, None), lib=lib)
-        del proto
         nbytes = lambda n: torch.empty(max(int(n), 1), dtype=torch.uint8, device=dev)
-        self.packed, self.pack_ws = nbytes(self.pack.pack_bytes), nbytes(self.pack.workspace_bytes)
-        self.ws = nbytes(self.plan.workspace_bytes)
         self.side = torch.cuda.Stream(dev)
+        self.exchange = exchange or ("residues" if part.world > 1 else "fp64")
+        lays = (la_, lb_, lc)
+        specs = [_dev.pack_spec(self.spec, *lays, operand=x, N=N, g=g, rounding=rounding, lib=lib)
+                 for x in (0, 1)]
+        if self.exchange == "residues":
+            pieces = [self._piece_spec(x, specs[x]) for x in (0, 1)]
+            if any(p is None for p in pieces):
+                self.exchange = "fp64"      # the piece index is not the slowest row mode
+        if self.exchange == "fp64":
+            self.A = torch.empty(part.gathered_shape(0), dtype=torch.float64, device=dev)
+            self.B = torch.empty(part.gathered_shape(1), dtype=torch.float64, device=dev)
+            self.pack = _dev.Pack(specs[0], lib=lib)
+            self.plan = _dev.Plan(self.spec, *lays, N=N, g=g, rounding=rounding,
+                                  packs=(self.pack, None), lib=lib)
+            self.packed, self.pack_ws = nbytes(self.pack.pack_bytes), nbytes(self.pack.workspace_bytes)
+        else:
+            self.slab = [_dev.Pack(sp, lib=lib) for sp in specs]          # keys of the plan's slots
+            self.piece = [_dev.Pack(sp, lib=lib) for sp in pieces]        # what this rank packs
+            self.plan = _dev.Plan(self.spec, *lays, N=N, g=g, rounding=rounding,
+                                  packs=tuple(self.slab), lib=lib)
+            self.pack_ws = [nbytes(pk.workspace_bytes) for pk in self.piece]
+            self.slab_rows = [pk.layout["r"] for pk in self.slab]
+            # this rank's piece inside each slab: its position in the group that shares the slab
+            self.pos = (part.ra, part.rb)
+            self.row0 = [self.pos[x] * self.piece[x].layout["r"] for x in (0, 1)]
+            for x in (0, 1):
+                n = part.pieces_b if x == 0 else part.pieces_a
+                assert self.slab_rows[x] == n * self.piece[x].layout["r"], "pieces do not tile the slab"
+            self._map_peers()
+            self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
+            low = self.plan.lowering
+            gg, NN = low["residue_group"], low["num_moduli"]
+            self.groups_of_planes = [(l0, min(gg, NN - l0)) for l0 in range(0, NN, gg)]
+        self.ws = nbytes(self.plan.workspace_bytes)
+
+    # -- set-up of the residue exchange ---------------------------------------------------------
+    def _piece_spec(self, x, slab_spec):
+        """The GIVEN pack spec of this rank's piece of operand x: the slab's classes and orders
+        without the piece-index label, on the piece's own (dense) descriptor. None when the piece
+        index is not the slowest row mode of the slab (its rows would not be contiguous)."""
+        from . import host
+        piece_label = ord("X" if x == 0 else "Y")
+        rows = [l for l in slab_spec.rows]
+        kept = [l for l, e in zip(slab_spec.tensor.label, slab_spec.tensor.extent) if e != 1]
+        if piece_label in kept and [l for l in rows if l in kept][-1] != piece_label:
+            return None
+        if piece_label in slab_spec.contracted or piece_label in slab_spec.batch:
+            return None
+        shape = self.part.shard_shape(x)
+        labels = tuple(ord(c) for c in (self.part.A if x == 0 else self.part.B))
+        return host.PackSpec(host.Desc(shape, host.dense_strides(shape), labels),
+                             tuple(slab_spec.contracted), tuple(slab_spec.batch),
+                             tuple(l for l in rows if l != piece_label), slab_spec.N,
+                             slab_spec.rounding, "GIVEN")
+
+    def _map_peers(self):
+        """Allocates the buffers peers write into (per operand: the packed slab and the gathered
+        FP64 slab; plain cudaMalloc allocations, so that an IPC handle names exactly the buffer)
+        and opens the other consumers' buffers through CUDA IPC WITH THIS RANK'S DEVICE CURRENT:
+        the mapping then belongs to this device's context and its kernels and copy engines may
+        write through it (a mapping opened under the exporting device's index, as tensor sharing
+        does, is not addressable from kernels of another device). Sets self.packed, self.A, self.B
+        and, per operand, the destination pointers (own buffer first)."""
+        from cuda.bindings import runtime as rt
+        from ._arrays import DeviceArray
+        torch, part = self._torch, self.part
+        ok = rt.cudaError_t.cudaSuccess
+
+        def check(err, what):
+            if err != ok:
+                raise RuntimeError(f"{what}: {err}")
+        self._rt, self._owned, self._opened = rt, [], []
+        shapes = [part.gathered_shape(0), part.gathered_shape(1)]
+        sizes = [(pk.pack_bytes + 255) // 256 * 256 or 256 for pk in self.slab] + \
+                [max(8 * math.prod(sh), 256) for sh in shapes]
+        for n in sizes:
+            err, ptr = rt.cudaMalloc(n)
+            check(err, "cudaMalloc of a shared buffer")
+            self._owned.append(int(ptr))
+        self.packed = [(self._owned[x], sizes[x]) for x in (0, 1)]
+        self.A, self.B = (torch.as_tensor(DeviceArray(self._owned[2 + x], shapes[x]), device=self.device)
+                          for x in (0, 1))
+        self.dests = [[self._owned[x]] for x in (0, 1)]          # packed slabs
+        self.fp64_dests = [[self._owned[2 + x]] for x in (0, 1)]  # gathered FP64 slabs
+        if part.world == 1:
+            return
+        mine = []
+        for ptr in self._owned:
+            err, handle = rt.cudaIpcGetMemHandle(ptr)
+            check(err, "cudaIpcGetMemHandle")
+            mine.append(bytes(handle.reserved))
+        everyone = [None] * part.world
+        self.dist.all_gather_object(everyone, mine)
+        sharers = (part.column_group(), part.row_group())     # ranks that consume the slab of A / B
+        for x in (0, 1):
+            for r in sharers[x]:
+                if r == part.rank:
+                    continue
+                for which, out in ((x, self.dests[x]), (2 + x, self.fp64_dests[x])):
+                    handle = rt.cudaIpcMemHandle_t()
+                    handle.reserved = everyone[r][which]
+                    err, ptr = rt.cudaIpcOpenMemHandle(handle, rt.cudaIpcMemLazyEnablePeerAccess)
+                    check(err, f"cudaIpcOpenMemHandle of rank {r}'s buffer")
+                    self._opened.append(int(ptr))
+                    out.append(int(ptr))
+        self.dist.barrier()
+
+    def _barrier(self):
+        if self.part.world > 1:
+            self.dist.all_reduce(self.tick)     # stream-ordered: no rank passes before all arrive
 
     def _gather(self, out, shard, grp):
         if grp is None:
@@ -169,24 +284,93 @@ class RankContraction:
         else:
             self.dist.all_gather_into_tensor(out.view(-1), shard.contiguous().view(-1), group=grp)
 
+    # -- the step ---------------------------------------------------------------------------------
     def __call__(self, shard_a, shard_b, C, alpha=1.0, beta=0.0):
         """C (this rank's tile, shape `tile_shape`) <- alpha A.B + beta C from the rank's pieces of
         A and B; enqueued on the current stream (and a side stream that joins it)."""
         torch = self._torch
         main = torch.cuda.current_stream()
         cols, rows = self.groups
-        self.side.wait_event(main.record_event())
-        with torch.cuda.stream(self.side):
-            self._gather(self.A, shard_a, cols[self.part.rb])
-            a_in = self.side.record_event()
-            self._gather(self.B, shard_b, rows[self.part.ra])
-            b_in = self.side.record_event()
-        main.wait_event(a_in)
-        self.pack.pack(self.A, self.packed, workspace=self.pack_ws, stream=main)
-        main.wait_event(b_in)
-        return self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
-                                  stream=main, packed=(self.packed, None))
+        if self.exchange == "fp64":
+            self.side.wait_event(main.record_event())
+            with torch.cuda.stream(self.side):
+                self._gather(self.A, shard_a, cols[self.part.rb])
+                a_in = self.side.record_event()
+                self._gather(self.B, shard_b, rows[self.part.ra])
+                b_in = self.side.record_event()
+            main.wait_event(a_in)
+            self.pack.pack(self.A, self.packed, workspace=self.pack_ws, stream=main)
+            main.wait_event(b_in)
+            return self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
+                                      stream=main, packed=(self.packed, None))
+        rt, s = self._rt, main.cuda_stream
+        shards = (shard_a, shard_b)
+        kind = rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice
+        side = self.side.cuda_stream
+
+        def copy2d(dst, src, off, rows, width, pitch):
+            if rows == 0 or width == 0:
+                return
+            err, = rt.cudaMemcpy2DAsync(dst + off, pitch, src + off, pitch, width, rows, kind, side)
+            if err != rt.cudaError_t.cudaSuccess:
+                raise RuntimeError(f"cudaMemcpy2DAsync to a peer: {err}")
+        self._barrier()                       # every rank is done with the previous step's slabs
+        packed_ev = []
+        for x in (0, 1):                      # own pieces into the own slab buffers: shifts, flags, all planes
+            if not shards[x].is_contiguous():
+                raise ValueError("the rank's pieces must be contiguous")
+            self.piece[x].scatter_ptr(shards[x].data_ptr(), self.slab_rows[x], self.row0[x],
+                                      self.dests[x][:1], self.slab[x].pack_bytes,
+                                      self.pack_ws[x].data_ptr(), self.pack_ws[x].numel(), s)
+            packed_ev.append(main.record_event())
+        # copy engines push the rows of the own pieces to the other consumers, group by group (the
+        # first group of A already while B is being packed)
+        arrived = []
+        for gi, (l0, mods) in enumerate(self.groups_of_planes):
+            for x in (0, 1):
+                if gi == 0:
+                    self.side.wait_event(packed_ev[x])
+                lay, R, b = self.slab[x].layout, self.slab_rows[x], self.slab[x].layout["b"]
+                rp, kh = self.piece[x].layout["r"], lay["k_hat"]
+                own = self.dests[x][0]
+                for dst in self.dests[x][1:]:
+                    if gi == 0:
+                        copy2d(dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
+                        copy2d(dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
+                    copy2d(dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b, rp * kh, R * kh)
+            arrived.append(self.side.record_event())
+        for x in (0, 1):                      # FP64 pieces: only the native path reads them
+            nb = shards[x].numel() * 8
+            for dst in self.fp64_dests[x]:
+                err, = rt.cudaMemcpyAsync(dst + self.pos[x] * nb, shards[x].data_ptr(), nb, kind, side)
+                if err != rt.cudaError_t.cudaSuccess:
+                    raise RuntimeError(f"cudaMemcpyAsync of an FP64 piece: {err}")
+        fp64_in = self.side.record_event()
+        packed = tuple(self.packed)
+        run = lambda part: self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
+                                              stream=main, packed=packed, part=part)
+        for gi, ev in enumerate(arrived):
+            main.wait_event(ev)
+            self._barrier()                   # every rank's planes of this group have landed
+            run(16 + gi)                      # GEMM of the group, while the next group's planes travel
+        run(3)                                # CRT of the emulated outputs
+        main.wait_event(fp64_in)
+        self._barrier()                       # every rank's FP64 pieces have landed
+        return run(2)                         # native path of non-finite rows and columns
 
     def close(self):
+        """Releases plans, packs and, with the residue exchange, the mappings and buffers (call it
+        on every rank, once no step is in flight anywhere)."""
         self.plan.close()
-        self.pack.close()
+        for pk in ([self.pack] if self.exchange == "fp64" else self.slab + self.piece):
+            pk.close()
+        if self.exchange == "residues" and getattr(self, "_owned", None):
+            self._torch.cuda.synchronize()
+            for ptr in self._opened:
+                self._rt.cudaIpcCloseMemHandle(ptr)
+            if self.part.world > 1:
+                self.dist.barrier()         # nobody frees a buffer a peer still has mapped
+            self.A = self.B = None
+            for ptr in self._owned:
+                self._rt.cudaFree(ptr)
+            self._owned, self._opened = [], []

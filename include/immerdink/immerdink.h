@@ -114,16 +114,23 @@ IMD_API imd_status_t imd_pack_scatter(imd_pack_t piece, const double* X, int64_t
                                       size_t dest_bytes, void* ws, size_t ws_bytes,
                                       cudaStream_t stream);
 
-/* imd_contract_packed in two parts (no counterpart in the reference; used by the multi-GPU driver
- * to start the emulated GEMM before the FP64 operands of other GPUs have arrived). part 0: the
- * whole call. part 1: everything except the outputs of the native path (outputs whose row of A or
- * column of B holds a non-finite entry): those elements of C are left untouched and A->data,
- * B->data are not read (they may be NULL). part 2: only those outputs, by the native path, from
- * the shifts and flags already in the packed buffers (for an in-line operand: in the workspace,
- * as part 1 of the same call left them); no GEMM runs. Parts 1 and 2 together, in this order and
- * with the same arguments, write exactly what part 0 writes. Same checks as
- * imd_contract_packed; part outside 0..2, or a part other than 0 on a plan whose call would not
- * run the emulated GEMM -> INVALID_VALUE. */
+/* imd_contract_packed in parts (no counterpart in the reference; used by the multi-GPU driver to
+ * start the GEMM of one residue group while the planes of the next are still arriving, and before
+ * the FP64 operands of other GPUs have arrived).
+ *   part 0       the whole call.
+ *   part 1       everything except the outputs of the native path (outputs whose row of A or
+ *                column of B holds a non-finite entry): those elements of C are left untouched
+ *                and A->data, B->data are not read (they may be NULL).
+ *   part 2       only those outputs, by the native path, from the shifts and flags already in
+ *                the packed buffers (in-line operand: in the workspace); no GEMM runs.
+ *   part 16 + i  only the GEMM of residue group i into the product planes of the workspace (for
+ *                an in-line operand also its shifts, when i = 0, and its residues of the group).
+ *   part 3       only the CRT of the emulated outputs, from the product planes in the workspace.
+ * Parts 16 + i for every group in order, then 3, then 2, with the same arguments and workspace,
+ * write exactly what part 0 writes; so do 1 then 2. Same checks as imd_contract_packed (the FP64
+ * pointers are required by parts 0 and 2 only); an unknown part, a group index beyond the
+ * plan's groups, or a part other than 0 on a plan whose call would not run the emulated GEMM ->
+ * INVALID_VALUE. */
 IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
                                               const imd_operand_t* A, const imd_operand_t* B,
                                               double beta, double* C, void* ws, size_t ws_bytes,

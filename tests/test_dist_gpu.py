@@ -8,7 +8,8 @@ from golden_util import same_bits
 pytestmark = pytest.mark.gpu
 
 
-def test_rank_contraction_world_1_equals_plain_call():
+@pytest.mark.parametrize("exchange", ["fp64", "residues"])
+def test_rank_contraction_world_1_equals_plain_call(exchange):
     import torch
     import immerdink_b200 as imd
     from immerdink_b200 import dist as idist
@@ -19,7 +20,8 @@ def test_rank_contraction_world_1_equals_plain_call():
     A = torch.from_numpy(rng.standard_normal(part.shard_shape(0))).cuda()
     B = torch.from_numpy(rng.standard_normal(part.shard_shape(1))).cuda()
     A[0, 1, 2, 3] = float("nan")
-    rc = idist.RankContraction(part, N=14, g=7)
+    rc = idist.RankContraction(part, N=14, g=7, exchange=exchange)
+    assert rc.exchange == exchange
     C1 = torch.full(rc.tile_shape, 3.0, dtype=torch.float64, device="cuda")
     for _ in range(2):
         rc(A, B, C1, alpha=0.5, beta=0.0)

@@ -375,5 +375,14 @@ def test_contract_packed_in_two_parts():
     plan.contract(dA, dB, C1, alpha=1.5, beta=2.0, workspace=ws, packed=tuple(bufs), part=2)
     torch.cuda.synchronize()
     assert same_bits(C1.cpu().numpy(), C0.cpu().numpy())
-    with pytest.raises(imd.InvalidValueError):
-        plan.contract(dA, dB, C1, workspace=ws, packed=tuple(bufs), part=3)
+    # group by group, then the CRT, then the native path (N = 10, g = 4: three groups)
+    planG = imd.Plan(spec, dA, dB, C0, N=N, g=4, packs=tuple(pks))
+    wg = torch.empty(planG.workspace_bytes, dtype=torch.uint8, device="cuda")
+    C2 = torch.full((m, n), 0.5, dtype=torch.float64, device="cuda")
+    for part in (16, 17, 18, 3, 2):
+        planG.contract(dA, dB, C2, alpha=1.5, beta=2.0, workspace=wg, packed=tuple(bufs), part=part)
+    torch.cuda.synchronize()
+    assert same_bits(C2.cpu().numpy(), C0.cpu().numpy())
+    for bad in (4, 15, 19, 16 + 20):
+        with pytest.raises(imd.InvalidValueError):
+            planG.contract(dA, dB, C2, workspace=wg, packed=tuple(bufs), part=bad)
