@@ -192,6 +192,8 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.index, self.samples, self.stop_flag, self.max_mhz = index, [], False, None
         self.error = None
+        self.ready = threading.Event()     # NVML initialised (its first call takes a while)
+        self.recording = False             # samples are kept only inside the timed region
 
     def run(self):
         try:
@@ -201,14 +203,24 @@ class ClockSampler(threading.Thread):
             idx = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
             h = nv.nvmlDeviceGetHandleByIndex(idx)
             self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self.ready.set()
             while not self.stop_flag:
-                self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
-                                     nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)))
-                time.sleep(0.002)
+                sample = (nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                          nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                if self.recording:
+                    self.samples.append(sample)
+                time.sleep(0.001)
         except Exception as exc:  # NVML missing: report it, never fail the benchmark
             self.error = repr(exc)
+        finally:
+            self.ready.set()
+
+    def begin(self):
+        self.ready.wait(timeout=10)
+        self.recording = True
 
     def summary(self):
+        self.recording = False
         self.stop_flag = True
         self.join(timeout=2)
         if not self.samples:
@@ -283,17 +295,18 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
 
     # ---- device-resident timing with per-phase events
     lib.lib.imd_prof_enable(64 * (args.steps + 1))
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(args.steps)]
     barrier()
+    sampler.begin()
     for s in range(args.steps):
         flush.fill_(s)  # evict the previous step's working set from L2 (outside the timed events)
         ev[s][0].record(stream)
