@@ -270,8 +270,19 @@ def run_ours(args, rank, world, local_rank):
         shard_a = synth(0, part.shard_shape(0), part.shard_start(0))
         shard_b = synth(1, part.shard_shape(1), part.shard_start(1))
         groups = idist.make_groups(world, dist)
-        rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
-                                      exchange=args.exchange)
+        try:
+            rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
+                                          exchange=args.exchange)
+            ok = torch.ones(1, device=dev)
+        except Exception as exc:   # e.g. CUDA IPC closed in this environment
+            print(f"rank {rank}: residue exchange unavailable ({exc!r})", file=sys.stderr)
+            rankc, ok = None, torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # all ranks take the same path
+        if ok.item() == 0:
+            if rankc is not None:
+                rankc.close()
+            rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
+                                          exchange="fp64")
         A, B, plan, run_spec = rankc.A, rankc.B, rankc.plan, rankc.spec
         Cd = torch.empty(rankc.tile_shape, dtype=torch.float64, device=dev)
 
