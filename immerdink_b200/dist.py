@@ -253,26 +253,46 @@ class RankContraction:
         self.fp64_dests = [[self._owned[2 + x]] for x in (0, 1)]  # gathered FP64 slabs
         if part.world == 1:
             return
-        mine = []
+        # Every rank goes through both collectives whatever fails locally, and all ranks fail together.
+        failure, mine = None, []
         for ptr in self._owned:
             err, handle = rt.cudaIpcGetMemHandle(ptr)
-            check(err, "cudaIpcGetMemHandle")
-            mine.append(bytes(handle.reserved))
+            if err != ok:
+                failure = failure or f"cudaIpcGetMemHandle: {err}"
+                mine.append(b"")
+            else:
+                mine.append(bytes(handle.reserved))
         everyone = [None] * part.world
         self.dist.all_gather_object(everyone, mine)
         sharers = (part.column_group(), part.row_group())     # ranks that consume the slab of A / B
         for x in (0, 1):
             for r in sharers[x]:
-                if r == part.rank:
+                if r == part.rank or failure:
                     continue
                 for which, out in ((x, self.dests[x]), (2 + x, self.fp64_dests[x])):
+                    if len(everyone[r][which]) != 64:
+                        failure = f"rank {r} exported no handle"
+                        break
                     handle = rt.cudaIpcMemHandle_t()
                     handle.reserved = everyone[r][which]
                     err, ptr = rt.cudaIpcOpenMemHandle(handle, rt.cudaIpcMemLazyEnablePeerAccess)
-                    check(err, f"cudaIpcOpenMemHandle of rank {r}'s buffer")
+                    if err != ok:
+                        failure = f"cudaIpcOpenMemHandle of rank {r}'s buffer: {err}"
+                        break
                     self._opened.append(int(ptr))
                     out.append(int(ptr))
-        self.dist.barrier()
+        bad = torch.tensor([1 if failure else 0], dtype=torch.int32, device=self.device)
+        self.dist.all_reduce(bad, op=self.dist.ReduceOp.MAX)
+        if int(bad.item()):
+            rt.cudaGetLastError()
+            for ptr in self._opened:
+                rt.cudaIpcCloseMemHandle(ptr)
+            self.dist.barrier()
+            for ptr in self._owned:
+                rt.cudaFree(ptr)
+            self._owned, self._opened = [], []
+            raise RuntimeError("residue exchange: peer buffers could not be mapped" +
+                               (f" ({failure})" if failure else " (on another rank)"))
 
     def _barrier(self):
         if self.part.world > 1:
