@@ -131,6 +131,28 @@ def gather(part, shard_a, shard_b, out_a, out_b, groups, dist):
             dist.all_gather_into_tensor(out.view(-1), shard.contiguous().view(-1), group=grp)
 
 
+def piece_pack_spec(part, x, slab_spec):
+    """The GIVEN pack spec of a rank's piece of operand x (0 = A, 1 = B): the classes and orders of
+    the slab's pack spec (`slab_spec`, of the gathered layout of Partition.plan_layouts) without the
+    piece-index label, on the piece's own dense descriptor. The rows of piece p are then rows
+    [p r, (p + 1) r) of the slab's packed layout. None when the piece index is not the slowest
+    row mode of the slab (the rows of a piece would not be contiguous in the slab)."""
+    from . import host
+    piece_label = ord("X" if x == 0 else "Y")
+    rows = list(slab_spec.rows)
+    kept = [l for l, e in zip(slab_spec.tensor.label, slab_spec.tensor.extent) if e != 1]
+    if piece_label in kept and [l for l in rows if l in kept][-1] != piece_label:
+        return None
+    if piece_label in slab_spec.contracted or piece_label in slab_spec.batch:
+        return None
+    shape = part.shard_shape(x)
+    labels = tuple(ord(c) for c in (part.A if x == 0 else part.B))
+    return host.PackSpec(host.Desc(shape, host.dense_strides(shape), labels),
+                         tuple(slab_spec.contracted), tuple(slab_spec.batch),
+                         tuple(l for l in rows if l != piece_label), slab_spec.N,
+                         slab_spec.rounding, "GIVEN")
+
+
 class RankContraction:
     """One rank's step of the partitioned contraction: exchange + compute, overlapped. Two ways to
     exchange (`exchange`):
@@ -172,7 +194,7 @@ class RankContraction:
         specs = [_dev.pack_spec(self.spec, *lays, operand=x, N=N, g=g, rounding=rounding, lib=lib)
                  for x in (0, 1)]
         if self.exchange == "residues":
-            pieces = [self._piece_spec(x, specs[x]) for x in (0, 1)]
+            pieces = [piece_pack_spec(part, x, specs[x]) for x in (0, 1)]
             if any(p is None for p in pieces):
                 self.exchange = "fp64"      # the piece index is not the slowest row mode
         if self.exchange == "fp64":
@@ -203,25 +225,6 @@ class RankContraction:
         self.ws = nbytes(self.plan.workspace_bytes)
 
     # -- set-up of the residue exchange ---------------------------------------------------------
-    def _piece_spec(self, x, slab_spec):
-        """The GIVEN pack spec of this rank's piece of operand x: the slab's classes and orders
-        without the piece-index label, on the piece's own (dense) descriptor. None when the piece
-        index is not the slowest row mode of the slab (its rows would not be contiguous)."""
-        from . import host
-        piece_label = ord("X" if x == 0 else "Y")
-        rows = [l for l in slab_spec.rows]
-        kept = [l for l, e in zip(slab_spec.tensor.label, slab_spec.tensor.extent) if e != 1]
-        if piece_label in kept and [l for l in rows if l in kept][-1] != piece_label:
-            return None
-        if piece_label in slab_spec.contracted or piece_label in slab_spec.batch:
-            return None
-        shape = self.part.shard_shape(x)
-        labels = tuple(ord(c) for c in (self.part.A if x == 0 else self.part.B))
-        return host.PackSpec(host.Desc(shape, host.dense_strides(shape), labels),
-                             tuple(slab_spec.contracted), tuple(slab_spec.batch),
-                             tuple(l for l in rows if l != piece_label), slab_spec.N,
-                             slab_spec.rounding, "GIVEN")
-
     def _map_peers(self):
         """Allocates the buffers peers write into (per operand: the packed slab and the gathered
         FP64 slab; plain cudaMalloc allocations, so that an IPC handle names exactly the buffer)

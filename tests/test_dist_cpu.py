@@ -91,3 +91,55 @@ def test_partition_rejects_labels_of_the_wrong_class():
         Partition(SPEC, EXT, 2, 0, "k", "b")
     with pytest.raises(ValueError):
         Partition(SPEC, dict(EXT, a=7), 2, 0, "a", "b")
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_pieces_packed_separately_tile_the_slab_pack(world):
+    """The residue exchange's data layout, on the CPU: the pack of every rank's piece (classes and
+    orders of the slab's pack without the piece-index label) holds exactly the rows of the slab's
+    pack at the piece's row offset; oracle packs, host-library layouts."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import imd_oracle as orc
+    from immerdink_b200 import dist as idist, host
+    A, B = _full_problem()
+    full = (A, B)
+    for rank in range(world):
+        part = idist.Partition(SPEC, EXT, world, rank, "a", "b")
+        spec, la, lb, lc = part.plan_layouts()
+        ins, outl = spec.split("->")
+        labs = ins.split(",") + [outl]
+        descs = tuple(host.Desc(l.shape, l.strides, tuple(ord(c) for c in lab))
+                      for l, lab in zip((la, lb, lc), labs))
+        for x, (lab, n_pieces, pos, group) in enumerate(((part.lb, part.pieces_b, part.ra, part.column_group()),
+                                                         (part.la, part.pieces_a, part.rb, part.row_group()))):
+            slab_spec = host.pack_desc_for(descs, operand=x, N=14, g=7)
+            piece_spec = idist.piece_pack_spec(part, x, slab_spec)
+            assert piece_spec is not None
+            sl, pl = host.pack_layout(slab_spec), host.pack_layout(piece_spec)
+            assert sl["r"] == n_pieces * pl["r"] and (sl["k"], sl["k_hat"], sl["b"], sl["format"]) == (
+                pl["k"], pl["k_hat"], pl["b"], pl["format"])
+            # the slab as the group's ranks gather it, and its pack by the oracle
+            axis = "kjbc".index(lab) if x == 0 else "kiac".index(lab)
+            piece = part.piece_b if x == 0 else part.piece_a
+            pieces = []
+            for r in group:
+                other = idist.Partition(SPEC, EXT, world, r, "a", "b")
+                s0 = other.shard_start(x)[lab]
+                pieces.append(np.ascontiguousarray(np.take(full[x], range(s0, s0 + piece), axis=axis)))
+            slab = np.stack(pieces)
+            sv = orc.pack_view(orc.Desc(list(slab_spec.tensor.extent), list(slab_spec.tensor.stride),
+                                        list(slab_spec.tensor.label)), slab_spec.contracted,
+                               slab_spec.batch, slab_spec.rows, "GIVEN", 14)
+            want = orc.pack(slab.reshape(-1), 0, sv)
+            pv = orc.pack_view(orc.Desc(list(piece_spec.tensor.extent), list(piece_spec.tensor.stride),
+                                        list(piece_spec.tensor.label)), piece_spec.contracted,
+                               piece_spec.batch, piece_spec.rows, "GIVEN", 14)
+            got = orc.pack(pieces[pos].reshape(-1), 0, pv)
+            R, rp, kh, b = sl["r"], pl["r"], sl["k_hat"], sl["b"]
+            assert b == 1
+            for l in range(14):
+                w = want[sl["res"][0] + (l * R + pos * rp) * kh:sl["res"][0] + (l * R + (pos + 1) * rp) * kh]
+                g_ = got[pl["res"][0] + l * rp * kh:pl["res"][0] + (l + 1) * rp * kh]
+                assert np.array_equal(w, g_), (world, rank, x, l)
+            assert np.array_equal(want[sl["sig"][0] + 2 * pos * rp:sl["sig"][0] + 2 * (pos + 1) * rp],
+                                  got[pl["sig"][0]:pl["sig"][0] + 2 * rp])
