@@ -238,29 +238,37 @@ class RankContraction:
         torch, part = self._torch, self.part
         ok = rt.cudaError_t.cudaSuccess
 
-        def check(err, what):
-            if err != ok:
-                raise RuntimeError(f"{what}: {err}")
         self._rt, self._owned, self._opened = rt, [], []
+        failure = None
         shapes = [part.gathered_shape(0), part.gathered_shape(1)]
         sizes = [(pk.pack_bytes + 255) // 256 * 256 or 256 for pk in self.slab] + \
                 [max(8 * math.prod(sh), 256) for sh in shapes]
         for n in sizes:
             err, ptr = rt.cudaMalloc(n)
-            check(err, "cudaMalloc of a shared buffer")
+            if err != ok:
+                failure = f"cudaMalloc of a shared buffer of {n} bytes: {err}"
+                break
             self._owned.append(int(ptr))
+        if failure and part.world == 1:
+            raise RuntimeError(failure)
+        while len(self._owned) < 4:
+            self._owned.append(0)           # placeholders: the ranks fail together below
         self.packed = [(self._owned[x], sizes[x]) for x in (0, 1)]
-        self.A, self.B = (torch.as_tensor(DeviceArray(self._owned[2 + x], shapes[x]), device=self.device)
-                          for x in (0, 1))
+        self.A = self.B = None
+        if not failure:
+            self.A, self.B = (torch.as_tensor(DeviceArray(self._owned[2 + x], shapes[x]), device=self.device)
+                              for x in (0, 1))
         self.dests = [[self._owned[x]] for x in (0, 1)]          # packed slabs
         self.fp64_dests = [[self._owned[2 + x]] for x in (0, 1)]  # gathered FP64 slabs
         if part.world == 1:
             return
         # Every rank goes through both collectives whatever fails locally, and all ranks fail together.
-        failure, mine = None, []
+        mine = []
         for ptr in self._owned:
-            err, handle = rt.cudaIpcGetMemHandle(ptr)
-            if err != ok:
+            err, handle = (ok, None) if failure else rt.cudaIpcGetMemHandle(ptr)
+            if failure:
+                mine.append(b"")
+            elif err != ok:
                 failure = failure or f"cudaIpcGetMemHandle: {err}"
                 mine.append(b"")
             else:
@@ -292,8 +300,10 @@ class RankContraction:
                 rt.cudaIpcCloseMemHandle(ptr)
             self.dist.barrier()
             for ptr in self._owned:
-                rt.cudaFree(ptr)
+                if ptr:
+                    rt.cudaFree(ptr)
             self._owned, self._opened = [], []
+            self.A = self.B = None
             raise RuntimeError("residue exchange: peer buffers could not be mapped" +
                                (f" ({failure})" if failure else " (on another rank)"))
 

@@ -17,13 +17,18 @@ LABELS = "abcdefgh"
 
 def draw(seed):
     rng = random.Random(seed)
-    la = rng.sample(LABELS, rng.randint(1, 4))
-    lb = rng.sample(LABELS, rng.randint(1, 4))
+    names = list(LABELS)
+    rng.shuffle(names)
+    take = lambda n: [names.pop() for _ in range(n)]
+    I, J, K, L = take(rng.randint(0, 2)), take(rng.randint(0, 2)), take(rng.randint(1, 2)), take(rng.randint(0, 1))
+    la, lb, lc = I + K + L, J + K + L, I + J + L
+    if rng.random() < 0.25 and names:
+        (la if rng.random() < 0.5 else lb).append(names.pop())         # summed over one operand only
+    for lst in (la, lb, lc):
+        rng.shuffle(lst)
     if rng.random() < 0.15:
         la.insert(rng.randrange(len(la) + 1), rng.choice(la))          # a diagonal of A
     pool = sorted(set(la) | set(lb))
-    lc = [x for x in pool if rng.random() < 0.6]
-    rng.shuffle(lc)
     ext = {x: rng.choice([1, 2, 3, 4, 5, 7, 17, 33]) for x in pool}
     tens = []
     for labels in (la, lb, lc):
@@ -85,7 +90,7 @@ def test_random_contraction(seed):
         return
     # the same contraction through packs of both operands (GIVEN: bit-identical)
     import torch
-    packs, packed = [], []
+    packs, packed, keep = [], [], []
     dev = [gu.dev_f64(b) for b in bufs]
     for x in (0, 1):
         spec = host.pack_desc_for(tuple(hd), operand=x, N=c["N"], g=c["g"], rounding=c["rounding"],
@@ -95,7 +100,16 @@ def test_random_contraction(seed):
         pk = imd.Pack(spec)
         buf, _ = _pack(pk, dev[x], bases[x])
         packs.append(pk)
+        keep.append(buf)            # the packed buffer must outlive the call
         packed.append(buf.arg())
+    specs = tuple(pk.spec for pk in packs)
+    lw = host.lowering(tuple(hd), N=c["N"], g=c["g"], rounding=c["rounding"], mode=c["mode"],
+                       packing=specs, check=False)
+    if lw["status"] == "PACK_MISMATCH":     # e.g. a K label that only the partner operand has
+        with pytest.raises(imd.PackMismatchError):
+            imd.Plan.from_descs(*hd, N=c["N"], g=c["g"], rounding=c["rounding"], mode=c["mode"],
+                                packs=tuple(packs))
+        return
     plan = imd.Plan.from_descs(*hd, N=c["N"], g=c["g"], rounding=c["rounding"], mode=c["mode"],
                                packs=tuple(packs))
     ws = gu.Workspace(plan.workspace_bytes)
@@ -106,6 +120,7 @@ def test_random_contraction(seed):
     torch.cuda.synchronize()
     assert ws.guards_intact()
     assert same_bits(gu.host_f64(dev[2]), want), ("packed", c)
+    assert all(b.guards_intact() for b in keep)
 
 
 def _pack(pk, X_dev, base):
