@@ -272,7 +272,7 @@ def run_ours(args, rank, world, local_rank):
         groups = idist.make_groups(world, dist)
         try:
             rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
-                                          exchange=args.exchange)
+                                          exchange=args.exchange, push_streams=args.push_streams)
             ok = torch.ones(1, device=dev)
         except Exception as exc:   # e.g. CUDA IPC closed in this environment
             print(f"rank {rank}: residue exchange unavailable ({exc!r})", file=sys.stderr)
@@ -512,7 +512,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and DGEMM legs")
     ap.add_argument("--slabs", type=int, default=8, help="slabs of the host-operand pipeline (e2e)")
     ap.add_argument("--exchange", default=None, choices=["residues", "fp64"],
-                    help="multi-GPU exchange (default: residues)")
+                    help="multi-GPU exchange (default: residues on 2 and 4 GPUs, fp64 on 8)")
+    ap.add_argument("--push-streams", type=int, default=1,
+                    help="streams of the residue exchange's peer copies")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

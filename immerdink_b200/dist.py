@@ -157,7 +157,7 @@ class RankContraction:
     """One rank's step of the partitioned contraction: exchange + compute, overlapped. Two ways to
     exchange (`exchange`):
 
-    "residues" (the default with more than one rank): every rank quantises only ITS pieces of A
+    "residues" (the default on 2 and 4 ranks): every rank quantises only ITS pieces of A
     and B, once, for all N moduli, and the pack kernels store the shifts, flags and int8 residue
     planes into its own packed slab buffers (`imd_pack_scatter`: the rows of a piece at their place
     in the slab); copy engines then push those rows into the packed slab buffers of the other
@@ -178,7 +178,7 @@ class RankContraction:
     the peers through CUDA IPC (cuda-python)."""
 
     def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
-                 exchange=None):
+                 exchange=None, push_streams=1):
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
@@ -189,7 +189,10 @@ class RankContraction:
         self.tile_shape = lc.shape
         nbytes = lambda n: torch.empty(max(int(n), 1), dtype=torch.uint8, device=dev)
         self.side = torch.cuda.Stream(dev)
-        self.exchange = exchange or ("residues" if part.world > 1 else "fp64")
+        # Defaults as measured (cc8000, whole steps): the residue exchange wins on 4 GPUs (2.48 against
+        # 2.81 ms) and ties on 2; on 8 the copy-engine pushes of one stream to three peers were far
+        # slower (5.2 against 1.79 ms), so 8 ranks exchange FP64.
+        self.exchange = exchange or ("residues" if part.world in (2, 4) else "fp64")
         lays = (la_, lb_, lc)
         specs = [_dev.pack_spec(self.spec, *lays, operand=x, N=N, g=g, rounding=rounding, lib=lib)
                  for x in (0, 1)]
@@ -218,6 +221,8 @@ class RankContraction:
                 n = part.pieces_b if x == 0 else part.pieces_a
                 assert self.slab_rows[x] == n * self.piece[x].layout["r"], "pieces do not tile the slab"
             self._map_peers()
+            # copies to different peers may go to different streams (copy engines); one by default
+            self.push_streams = [torch.cuda.Stream(dev) for _ in range(max(1, int(push_streams)))]
             self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
             low = self.plan.lowering
             gg, NN = low["residue_group"], low["num_moduli"]
@@ -339,12 +344,14 @@ class RankContraction:
         rt, s = self._rt, main.cuda_stream
         shards = (shard_a, shard_b)
         kind = rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice
-        side = self.side.cuda_stream
+        # one stream per destination: copies to different peers run on different copy engines
+        pushes = self.push_streams
 
-        def copy2d(dst, src, off, rows, width, pitch):
+        def copy2d(j, dst, src, off, rows, width, pitch):
             if rows == 0 or width == 0:
                 return
-            err, = rt.cudaMemcpy2DAsync(dst + off, pitch, src + off, pitch, width, rows, kind, side)
+            err, = rt.cudaMemcpy2DAsync(dst + off, pitch, src + off, pitch, width, rows, kind,
+                                        pushes[j % len(pushes)].cuda_stream)
             if err != rt.cudaError_t.cudaSuccess:
                 raise RuntimeError(f"cudaMemcpy2DAsync to a peer: {err}")
         self._barrier()                       # every rank is done with the previous step's slabs
@@ -362,32 +369,37 @@ class RankContraction:
         for gi, (l0, mods) in enumerate(self.groups_of_planes):
             for x in (0, 1):
                 if gi == 0:
-                    self.side.wait_event(packed_ev[x])
+                    for st in pushes:
+                        st.wait_event(packed_ev[x])
                 lay, R, b = self.slab[x].layout, self.slab_rows[x], self.slab[x].layout["b"]
                 rp, kh = self.piece[x].layout["r"], lay["k_hat"]
                 own = self.dests[x][0]
-                for dst in self.dests[x][1:]:
+                for j, dst in enumerate(self.dests[x][1:]):
                     if gi == 0:
-                        copy2d(dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
-                        copy2d(dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
-                    copy2d(dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b, rp * kh, R * kh)
-            arrived.append(self.side.record_event())
+                        copy2d(j, dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
+                        copy2d(j, dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
+                    copy2d(j, dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b, rp * kh,
+                           R * kh)
+            arrived.append([st.record_event() for st in pushes])
         for x in (0, 1):                      # FP64 pieces: only the native path reads them
             nb = shards[x].numel() * 8
-            for dst in self.fp64_dests[x]:
-                err, = rt.cudaMemcpyAsync(dst + self.pos[x] * nb, shards[x].data_ptr(), nb, kind, side)
+            for j, dst in enumerate(self.fp64_dests[x]):
+                err, = rt.cudaMemcpyAsync(dst + self.pos[x] * nb, shards[x].data_ptr(), nb, kind,
+                                          pushes[j % len(pushes)].cuda_stream)
                 if err != rt.cudaError_t.cudaSuccess:
                     raise RuntimeError(f"cudaMemcpyAsync of an FP64 piece: {err}")
-        fp64_in = self.side.record_event()
+        fp64_in = [st.record_event() for st in pushes]
         packed = tuple(self.packed)
         run = lambda part: self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
                                               stream=main, packed=packed, part=part)
-        for gi, ev in enumerate(arrived):
-            main.wait_event(ev)
+        for gi, evs in enumerate(arrived):
+            for ev in evs:
+                main.wait_event(ev)
             self._barrier()                   # every rank's planes of this group have landed
             run(16 + gi)                      # GEMM of the group, while the next group's planes travel
         run(3)                                # CRT of the emulated outputs
-        main.wait_event(fp64_in)
+        for ev in fp64_in:
+            main.wait_event(ev)
         self._barrier()                       # every rank's FP64 pieces have landed
         return run(2)                         # native path of non-finite rows and columns
 
