@@ -272,7 +272,8 @@ def run_ours(args, rank, world, local_rank):
         groups = idist.make_groups(world, dist)
         try:
             rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
-                                          exchange=args.exchange, push_streams=args.push_streams)
+                                          exchange=args.exchange, push_streams=args.push_streams,
+                                          sync=args.sync)
             ok = torch.ones(1, device=dev)
         except Exception as exc:   # e.g. CUDA IPC closed in this environment
             print(f"rank {rank}: residue exchange unavailable ({exc!r})", file=sys.stderr)
@@ -392,6 +393,27 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_ms = float(t_e2e.item())
     exchange_ms = resident_ms = 0.0
+    parity = None
+    if world > 1:
+        # every rank checks the outputs of one sampled block (CPU oracle, full k) that fall into its tile
+        _, _, out, coff = cpu_sample(prob, 192, 192)
+        labels_c = prob.labels[2]
+        idx = np.unravel_index(coff.reshape(-1), prob.shape(2, False))
+        local_shape = [part.local[c] for c in labels_c]
+        inside, loc = np.ones(coff.size, dtype=bool), []
+        for d, c in enumerate(labels_c):
+            v = idx[d] - part.start.get(c, 0)
+            inside &= (v >= 0) & (v < local_shape[d])
+            loc.append(v)
+        flat = np.ravel_multi_index([v[inside] for v in loc], local_shape)
+        got = Cd.reshape(-1)[torch.from_numpy(flat).to(dev)].cpu().numpy()
+        same = np.array_equal(got.view(np.uint64), out.reshape(-1)[inside].view(np.uint64))
+        agree = torch.tensor([int(same)], dtype=torch.int64, device=dev)
+        count = torch.tensor([int(inside.sum())], dtype=torch.int64, device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        dist.all_reduce(count, op=dist.ReduceOp.SUM)
+        parity = dict(outputs=int(count.item()), bit_exact=bool(agree.item()),
+                      how="each rank compares the sampled outputs inside its tile with the CPU oracle")
     if exchange is not None:
         def timed(fn, reps=5):
             x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -473,6 +495,12 @@ def run_ours(args, rank, world, local_rank):
                               "bytes of one GEMM launch (algorithmic: both operands' planes once + product "
                               "planes once = 1.34e9 at cc8000)"),
                 device_error=int(err))
+    if parity is not None:
+        line["parity_sample"] = parity
+    if world > 1 and rankc.exchange == "residues":
+        line["config"]["exchange"] = dict(kind="residues", sync=rankc.sync, push_streams=len(rankc.push_streams))
+    elif world > 1:
+        line["config"]["exchange"] = dict(kind="fp64")
     if world == 1 and not args.no_cpu:
         # DGEMM on the same GPU, same GEMM view
         n = low["m"]
@@ -513,6 +541,8 @@ def main():
     ap.add_argument("--slabs", type=int, default=8, help="slabs of the host-operand pipeline (e2e)")
     ap.add_argument("--exchange", default=None, choices=["residues", "fp64"],
                     help="multi-GPU exchange (default: residues on 2 and 4 GPUs, fp64 on 8)")
+    ap.add_argument("--sync", default="barrier", choices=["barrier", "flags"],
+                    help="residue exchange: how consumers learn that planes have landed")
     ap.add_argument("--push-streams", type=int, default=1,
                     help="streams of the residue exchange's peer copies")
     args = ap.parse_args()

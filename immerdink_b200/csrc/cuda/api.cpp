@@ -359,6 +359,20 @@ imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const imd_operan
   return imd_contract_packed_part(plan, alpha, A, B, beta, C, ws, ws_bytes, stream, 0);
 }
 
+/* Bounded wait on flags that a peer's copies set (extension; see the header). */
+imd_status_t imd_wait_flags(const unsigned int* const* flags, int num_flags, unsigned int expect,
+                            uint64_t max_polls, cudaStream_t stream) {
+  if (num_flags == 0) return IMD_STATUS_SUCCESS;
+  if (flags == nullptr || num_flags < 0 || num_flags > imd::kMaxWaitFlags)
+    return IMD_STATUS_INVALID_VALUE;
+  for (int i = 0; i < num_flags; ++i) {
+    if (flags[i] == nullptr) return IMD_STATUS_INVALID_VALUE;
+    if (reinterpret_cast<uintptr_t>(flags[i]) % 4 != 0) return IMD_STATUS_MISALIGNED;
+  }
+  const unsigned long long limit = max_polls ? max_polls : 4000000ull;  /* about a second */
+  return imd::enqueue_wait_flags(flags, num_flags, expect, limit, stream);
+}
+
 /* ---- verification hooks (not part of the drop-in ABI) ---------------------------------------- */
 /* 1: run the slow exact int8 GEMM instead of the tensor-core kernel in later calls (cross-check). */
 IMD_API int imd_test_use_reference_gemm(int on) {

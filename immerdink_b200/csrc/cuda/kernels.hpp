@@ -64,6 +64,12 @@ imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables
                                   cudaStream_t stream);
 imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stream);
 
+// Bounded wait (one launch of one warp) until every flags[i] (device addresses, n <= kMaxWaitFlags)
+// holds `expect`; gives up after `limit` polls per flag and sets bit 2 of the device error word.
+constexpr int kMaxWaitFlags = 32;
+imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigned int expect,
+                                unsigned long long limit, cudaStream_t stream);
+
 // Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.
 bool& use_reference_gemm();
 // Verification switch for the tensor-core kernel: 0 = chosen by shape, 1 = one CTA per 128 x 256

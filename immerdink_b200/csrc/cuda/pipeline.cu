@@ -976,6 +976,46 @@ imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables
   return IMD_STATUS_SUCCESS;
 }
 
+// ---- bounded wait on flags --------------------------------------------------------------------------
+// For exchanges in which a peer's copy engine writes data into this GPU's memory and then a 32-bit
+// flag: one thread per flag polls (system-scope acquire loads) until the flag holds `expect`, for at
+// most `limit` polls; a thread that gives up sets bit 2 of the device error word and returns, so
+// the stream always moves on. Kernels launched after this one see the data the flags announce.
+namespace {
+
+struct WaitParams {
+  const unsigned int* flag[kMaxWaitFlags];
+  int n;
+  unsigned int expect;
+  unsigned long long limit;
+  unsigned int* error_word;
+};
+
+__global__ void k_wait_flags(WaitParams p) {
+  const int i = threadIdx.x;
+  if (i >= p.n) return;
+  for (unsigned long long it = 0; it < p.limit; ++it) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flag[i]) : "memory");
+    if (v == p.expect) return;
+    __nanosleep(200);
+  }
+  atomicOr(p.error_word, 4u);
+}
+
+}  // namespace
+
+imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigned int expect,
+                                unsigned long long limit, cudaStream_t stream) {
+  WaitParams p;
+  for (int i = 0; i < kMaxWaitFlags; ++i) p.flag[i] = i < n ? flags[i] : nullptr;
+  p.n = n, p.expect = expect, p.limit = limit;
+  p.error_word = device_error_word();
+  if (p.error_word == nullptr) return IMD_STATUS_CUDA_ERROR;
+  k_wait_flags<<<1, kMaxWaitFlags, 0, stream>>>(p);
+  return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
 // ---- built-in workspace ---------------------------------------------------------------------------
 // A fixed workspace that lives in the library image, for callers that are not in a position to
 // allocate device memory. The name below is only a handle on the host side: its device address is

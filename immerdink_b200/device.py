@@ -66,6 +66,17 @@ def load_library(path=None):
     return path if isinstance(path, _capi.Library) else _capi.load(path)
 
 
+def wait_flags(flags, expect, *, max_polls=0, stream=0, lib=None):
+    """imd_wait_flags: enqueue a bounded wait on `stream` until every 32-bit word at the device
+    addresses `flags` (at most 32) holds `expect`. A wait that runs out (max_polls polls per flag;
+    0 = about a second) sets bit 2 of the device error word instead of blocking the stream."""
+    lib = load_library(lib)
+    arr = (ct.c_void_p * max(len(flags), 1))(*[int(f) for f in flags])
+    st = lib.lib.imd_wait_flags(arr, len(flags), int(expect), int(max_polls), stream)
+    if st:
+        raise _error(st, "imd_wait_flags")
+
+
 class Layout(namedtuple("Layout", "shape strides")):
     """Extents and ELEMENT strides of an operand (None = dense), to plan before arrays exist."""
 

@@ -19,6 +19,7 @@ import math
 from dataclasses import dataclass
 
 GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
+_POSITIONS, _SLOTS = 8, 16      # flag words per operand: producers sharing a slab x (residue groups + FP64)
 
 
 @dataclass
@@ -169,6 +170,13 @@ class RankContraction:
         main   barrier | pack own pieces | barrier, GEMM group 0 | barrier, GEMM group 1 | CRT | barrier, native path
         side                             | push group 0 | push group 1 ...... | push FP64 pieces |
 
+    How a consumer learns that a group's planes have landed (`sync`): "barrier" = every rank waits
+    for its own copies and the ranks meet in a tiny NCCL all-reduce per group; "flags" = after the
+    copies to a consumer the producer's stream copies the step's number into a flag word in that
+    consumer's memory, and the consumer's stream polls its flag words with a bounded wait
+    (imd_wait_flags: a wait that runs out sets the device error word, the stream moves on); one
+    all-reduce per step remains, before the slabs are overwritten.
+
     "fp64": the slabs are all-gathered as FP64 (NCCL, side stream), A is packed as soon as its
     slab is complete and while B's is still arriving, B is quantised in line.
 
@@ -178,7 +186,7 @@ class RankContraction:
     the peers through CUDA IPC (cuda-python)."""
 
     def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
-                 exchange=None, push_streams=1):
+                 exchange=None, push_streams=1, sync="barrier"):
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
@@ -224,6 +232,13 @@ class RankContraction:
             # copies to different peers may go to different streams (copy engines); one by default
             self.push_streams = [torch.cuda.Stream(dev) for _ in range(max(1, int(push_streams)))]
             self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
+            if sync not in ("barrier", "flags"):
+                raise ValueError("sync must be 'barrier' or 'flags'")
+            self.sync = sync
+            self.lib = self.slab[0].lib
+            # flags: the value a producer copies into a consumer's flag word after its planes
+            self.values = torch.arange(1 << 16, dtype=torch.int32, device=dev)
+            self.step = 0
             low = self.plan.lowering
             gg, NN = low["residue_group"], low["num_moduli"]
             self.groups_of_planes = [(l0, min(gg, NN - l0)) for l0 in range(0, NN, gg)]
@@ -247,7 +262,7 @@ class RankContraction:
         failure = None
         shapes = [part.gathered_shape(0), part.gathered_shape(1)]
         sizes = [(pk.pack_bytes + 255) // 256 * 256 or 256 for pk in self.slab] + \
-                [max(8 * math.prod(sh), 256) for sh in shapes]
+                [max(8 * math.prod(sh), 256) for sh in shapes] + [4 * 2 * _POSITIONS * _SLOTS]
         for n in sizes:
             err, ptr = rt.cudaMalloc(n)
             if err != ok:
@@ -256,8 +271,12 @@ class RankContraction:
             self._owned.append(int(ptr))
         if failure and part.world == 1:
             raise RuntimeError(failure)
-        while len(self._owned) < 4:
+        while len(self._owned) < 5:
             self._owned.append(0)           # placeholders: the ranks fail together below
+        if not failure:
+            err, = rt.cudaMemset(self._owned[4], 0, sizes[4])
+            if err != ok:
+                failure = f"cudaMemset of the flag words: {err}"
         self.packed = [(self._owned[x], sizes[x]) for x in (0, 1)]
         self.A = self.B = None
         if not failure:
@@ -265,6 +284,8 @@ class RankContraction:
                               for x in (0, 1))
         self.dests = [[self._owned[x]] for x in (0, 1)]          # packed slabs
         self.fp64_dests = [[self._owned[2 + x]] for x in (0, 1)]  # gathered FP64 slabs
+        self.flags = self._owned[4]                              # [operand][producer position][slot] words
+        self.flag_dests = [[], []]                               # the other consumers' flag words
         if part.world == 1:
             return
         # Every rank goes through both collectives whatever fails locally, and all ranks fail together.
@@ -285,7 +306,7 @@ class RankContraction:
             for r in sharers[x]:
                 if r == part.rank or failure:
                     continue
-                for which, out in ((x, self.dests[x]), (2 + x, self.fp64_dests[x])):
+                for which, out in ((x, self.dests[x]), (2 + x, self.fp64_dests[x]), (4, self.flag_dests[x])):
                     if len(everyone[r][which]) != 64:
                         failure = f"rank {r} exported no handle"
                         break
@@ -341,19 +362,45 @@ class RankContraction:
             main.wait_event(b_in)
             return self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
                                       stream=main, packed=(self.packed, None))
+        from .device import wait_flags as _dev_wait
         rt, s = self._rt, main.cuda_stream
         shards = (shard_a, shard_b)
         kind = rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice
-        # one stream per destination: copies to different peers run on different copy engines
+        # copies to different peers may go to different streams; all copies to one peer share one
         pushes = self.push_streams
+        flags = self.sync == "flags" and self.part.world > 1
+        self.step = self.step % 65535 + 1     # 1..65535: never the value of an untouched flag word
+        tick = self.step
 
-        def copy2d(j, dst, src, off, rows, width, pitch):
+        def copy(j, dst, src, nbytes):
+            err, = rt.cudaMemcpyAsync(dst, src, nbytes, kind, pushes[j % len(pushes)].cuda_stream)
+            if err != rt.cudaError_t.cudaSuccess:
+                raise RuntimeError(f"cudaMemcpyAsync to a peer: {err}")
+
+        def copy_rows(j, dst, src, off, rows, width, pitch):
+            """`rows` runs of `width` bytes, `pitch` apart: contiguous copies (a few large runs;
+            pitched copies between peers were several times slower)."""
             if rows == 0 or width == 0:
                 return
-            err, = rt.cudaMemcpy2DAsync(dst + off, pitch, src + off, pitch, width, rows, kind,
-                                        pushes[j % len(pushes)].cuda_stream)
-            if err != rt.cudaError_t.cudaSuccess:
-                raise RuntimeError(f"cudaMemcpy2DAsync to a peer: {err}")
+            if width == pitch:
+                rows, width = 1, rows * width
+            for r in range(rows):
+                copy(j, dst + off + r * pitch, src + off + r * pitch, width)
+
+        def word(x, position, slot):          # offset of a flag word inside a rank's flag buffer
+            return 4 * ((x * _POSITIONS + position) * _SLOTS + slot)
+
+        def announce(x, j, slot):             # after the copies to consumer j of slab x: its flag word
+            if flags:
+                copy(j, self.flag_dests[x][j] + word(x, self.pos[x], slot),
+                     self.values.data_ptr() + 4 * tick, 4)
+
+        def await_(slot):                     # every other producer's copies of this slot have landed here
+            ptrs = [self.flags + word(x, p, slot)
+                    for x, n in ((0, self.part.pieces_b), (1, self.part.pieces_a))
+                    for p in range(n) if p != self.pos[x]]
+            _dev_wait(ptrs, tick, stream=s, lib=self.lib)
+
         self._barrier()                       # every rank is done with the previous step's slabs
         packed_ev = []
         for x in (0, 1):                      # own pieces into the own slab buffers: shifts, flags, all planes
@@ -376,31 +423,37 @@ class RankContraction:
                 own = self.dests[x][0]
                 for j, dst in enumerate(self.dests[x][1:]):
                     if gi == 0:
-                        copy2d(j, dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
-                        copy2d(j, dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
-                    copy2d(j, dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b, rp * kh,
-                           R * kh)
-            arrived.append([st.record_event() for st in pushes])
+                        copy_rows(j, dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
+                        copy_rows(j, dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
+                    copy_rows(j, dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b,
+                              rp * kh, R * kh)
+                    announce(x, j, gi)
+            arrived.append(None if flags else [st.record_event() for st in pushes])
         for x in (0, 1):                      # FP64 pieces: only the native path reads them
             nb = shards[x].numel() * 8
-            for j, dst in enumerate(self.fp64_dests[x]):
-                err, = rt.cudaMemcpyAsync(dst + self.pos[x] * nb, shards[x].data_ptr(), nb, kind,
-                                          pushes[j % len(pushes)].cuda_stream)
-                if err != rt.cudaError_t.cudaSuccess:
-                    raise RuntimeError(f"cudaMemcpyAsync of an FP64 piece: {err}")
+            for j, dst in enumerate(self.fp64_dests[x][1:]):
+                copy(j, dst + self.pos[x] * nb, shards[x].data_ptr(), nb)
+                announce(x, j, _SLOTS - 1)
+            copy(0, self.fp64_dests[x][0] + self.pos[x] * nb, shards[x].data_ptr(), nb)   # the own buffer
         fp64_in = [st.record_event() for st in pushes]
         packed = tuple(self.packed)
         run = lambda part: self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
                                               stream=main, packed=packed, part=part)
         for gi, evs in enumerate(arrived):
-            for ev in evs:
-                main.wait_event(ev)
-            self._barrier()                   # every rank's planes of this group have landed
+            if flags:
+                await_(gi)                    # the other producers' planes of this group have landed here
+            else:
+                for ev in evs:
+                    main.wait_event(ev)
+                self._barrier()               # every rank's planes of this group have landed
             run(16 + gi)                      # GEMM of the group, while the next group's planes travel
         run(3)                                # CRT of the emulated outputs
-        for ev in fp64_in:
+        for ev in fp64_in:                    # the own pushes are done before the next step repacks
             main.wait_event(ev)
-        self._barrier()                       # every rank's FP64 pieces have landed
+        if flags:
+            await_(_SLOTS - 1)
+        else:
+            self._barrier()                   # every rank's FP64 pieces have landed
         return run(2)                         # native path of non-finite rows and columns
 
     def close(self):

@@ -114,6 +114,18 @@ IMD_API imd_status_t imd_pack_scatter(imd_pack_t piece, const double* X, int64_t
                                       size_t dest_bytes, void* ws, size_t ws_bytes,
                                       cudaStream_t stream);
 
+/* Bounded wait for data that arrives by copies from other GPUs (no counterpart in the reference;
+ * used by the multi-GPU driver). A producer copies data into this GPU's memory and then, in the
+ * same stream, a 32-bit value into a flag word next to it. This call enqueues on `stream` one
+ * small kernel that polls the num_flags (0..32) words flags[i] (device addresses, read at the
+ * call) until each holds `expect`; work enqueued on `stream` afterwards sees the announced data.
+ * The wait is bounded: after max_polls polls of a flag (0 = the default, about a second) the
+ * kernel gives up, sets bit 2 (value 4) of the device error word (imd_test_device_error) and
+ * returns, so the stream always moves on. Checks: NULL -> INVALID_VALUE; num_flags outside 0..32
+ * -> INVALID_VALUE; a flag address that is not 4-byte aligned -> MISALIGNED. */
+IMD_API imd_status_t imd_wait_flags(const unsigned int* const* flags, int num_flags,
+                                    unsigned int expect, uint64_t max_polls, cudaStream_t stream);
+
 /* imd_contract_packed in parts (no counterpart in the reference; used by the multi-GPU driver to
  * start the GEMM of one residue group while the planes of the next are still arriving, and before
  * the FP64 operands of other GPUs have arrived).

@@ -31,3 +31,30 @@ def test_rank_contraction_world_1_equals_plain_call(exchange):
     torch.cuda.synchronize()
     assert same_bits(C1.reshape(C0.shape).cpu().numpy(), C0.cpu().numpy())
     rc.close()
+
+
+def test_wait_flags_passes_when_set_and_gives_up_when_not():
+    """The bounded wait the residue exchange uses: flags that hold the expected value let the
+    stream through; a flag nothing sets makes the wait run out, which sets bit 2 of the device
+    error word and leaves the context usable."""
+    import torch
+    import immerdink_b200 as imd
+    from immerdink_b200 import device
+    lib = imd.load_library()
+    lib.lib.imd_test_device_error()                       # clear
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    flags[3] = 7
+    flags[40] = 7
+    base = flags.data_ptr()
+    stream = torch.cuda.current_stream().cuda_stream
+    device.wait_flags([base + 4 * 3, base + 4 * 40], 7, stream=stream)
+    device.wait_flags([], 7, stream=stream)               # nothing to wait for
+    assert lib.lib.imd_test_device_error() == 0
+    device.wait_flags([base + 4 * 3, base + 4 * 5], 7, max_polls=50, stream=stream)   # word 5 stays 0
+    assert lib.lib.imd_test_device_error() == 4
+    assert lib.lib.imd_test_device_error() == 0           # sticky until read, then clear
+    assert int((flags + 1).sum().item()) == 64 + 14       # the context still works
+    with pytest.raises(imd.InvalidValueError):
+        device.wait_flags([base] * 33, 7, stream=stream)
+    with pytest.raises(imd.MisalignedError):
+        device.wait_flags([base + 2], 7, stream=stream)
