@@ -532,10 +532,13 @@ class Plan:
             ops.append(_capi.Operand(data, p, n, pk._h))
         return ct.byref(ops[0]), ct.byref(ops[1])
 
-    def contract_ptr(self, alpha, A, B, beta, C, ws, ws_bytes, stream=0, packed=None):
+    def contract_ptr(self, alpha, A, B, beta, C, ws, ws_bytes, stream=0, packed=None, part=0):
         """imd_contract with raw integers: only the C checks. packed = ((ptr, nbytes) or None,
-        ...) for a packed plan."""
-        if self._packed:
+        ...) for a packed plan; part as in contract()."""
+        if self._packed and part:
+            st = self.lib.lib.imd_contract_packed_part(self._h, alpha, *self._operands(A, B, packed, stream),
+                                                       beta, C, ws, ws_bytes, stream, int(part))
+        elif self._packed:
             st = self._fn(self._h, alpha, *self._operands(A, B, packed, stream), beta, C, ws,
                           ws_bytes, stream)
         else:

@@ -190,6 +190,7 @@ class RankContraction:
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
+        self.trace = None
         self.groups = groups if groups is not None else ({part.rb: None}, {part.ra: None})
         dev = torch.device("cuda", torch.cuda.current_device())
         self.device = dev
@@ -333,6 +334,14 @@ class RankContraction:
             raise RuntimeError("residue exchange: peer buffers could not be mapped" +
                                (f" ({failure})" if failure else " (on another rank)"))
 
+    def _mark(self, label, stream):
+        """With `self.trace` a list: appends (label, timing event recorded on `stream`), to lay out
+        one step on a time line afterwards."""
+        if self.trace is not None:
+            ev = self._torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            self.trace.append((label, ev))
+
     def _barrier(self):
         if self.part.world > 1:
             self.dist.all_reduce(self.tick)     # stream-ordered: no rank passes before all arrive
@@ -401,20 +410,27 @@ class RankContraction:
                     for p in range(n) if p != self.pos[x]]
             _dev_wait(ptrs, tick, stream=s, lib=self.lib)
 
+        self._mark("begin", main)
         self._barrier()                       # every rank is done with the previous step's slabs
-        packed_ev = []
-        for x in (0, 1):                      # own pieces into the own slab buffers: shifts, flags, all planes
-            if not shards[x].is_contiguous():
-                raise ValueError("the rank's pieces must be contiguous")
+        self._mark("all ranks in", main)
+        # the operand whose slab has more consumers is packed first: its planes travel while the
+        # other operand is being packed
+        order = (1, 0) if self.part.pb > self.part.pa else (0, 1)
+        packed_ev = [None, None]
+        for x in order:                       # own pieces into the own slab buffers: shifts, flags, all planes
+            if (tuple(shards[x].shape) != tuple(self.part.shard_shape(x)) or not shards[x].is_contiguous()
+                    or shards[x].dtype != torch.float64):
+                raise ValueError("the rank's pieces must be dense FP64 arrays of Partition.shard_shape")
             self.piece[x].scatter_ptr(shards[x].data_ptr(), self.slab_rows[x], self.row0[x],
                                       self.dests[x][:1], self.slab[x].pack_bytes,
                                       self.pack_ws[x].data_ptr(), self.pack_ws[x].numel(), s)
-            packed_ev.append(main.record_event())
+            packed_ev[x] = main.record_event()
+            self._mark(f"packed {'AB'[x]}", main)
         # copy engines push the rows of the own pieces to the other consumers, group by group (the
-        # first group of A already while B is being packed)
+        # first group of the operand packed first already while the other is being packed)
         arrived = []
         for gi, (l0, mods) in enumerate(self.groups_of_planes):
-            for x in (0, 1):
+            for x in order:
                 if gi == 0:
                     for st in pushes:
                         st.wait_event(packed_ev[x])
@@ -429,6 +445,7 @@ class RankContraction:
                               rp * kh, R * kh)
                     announce(x, j, gi)
             arrived.append(None if flags else [st.record_event() for st in pushes])
+            self._mark(f"pushed group {gi}", pushes[0])
         for x in (0, 1):                      # FP64 pieces: only the native path reads them
             nb = shards[x].numel() * 8
             for j, dst in enumerate(self.fp64_dests[x][1:]):
@@ -436,9 +453,16 @@ class RankContraction:
                 announce(x, j, _SLOTS - 1)
             copy(0, self.fp64_dests[x][0] + self.pos[x] * nb, shards[x].data_ptr(), nb)   # the own buffer
         fp64_in = [st.record_event() for st in pushes]
+        self._mark("pushed fp64", pushes[0])
         packed = tuple(self.packed)
-        run = lambda part: self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
-                                              stream=main, packed=packed, part=part)
+        if tuple(C.shape) != tuple(self.tile_shape) or not C.is_contiguous() or C.dtype != torch.float64:
+            raise ValueError("C must be the rank's dense FP64 tile")
+        ptrs = (self.A.data_ptr(), self.B.data_ptr(), C.data_ptr(), self.ws.data_ptr(), self.ws.numel())
+
+        def run(part):                        # raw pointers: the C checks only, little host time per call
+            self.plan.contract_ptr(alpha, ptrs[0], ptrs[1], beta, ptrs[2], ptrs[3], ptrs[4], s,
+                                   packed=packed, part=part)
+            return C
         for gi, evs in enumerate(arrived):
             if flags:
                 await_(gi)                    # the other producers' planes of this group have landed here
@@ -446,15 +470,21 @@ class RankContraction:
                 for ev in evs:
                     main.wait_event(ev)
                 self._barrier()               # every rank's planes of this group have landed
+            self._mark(f"group {gi} in", main)
             run(16 + gi)                      # GEMM of the group, while the next group's planes travel
+            self._mark(f"gemm {gi}", main)
         run(3)                                # CRT of the emulated outputs
+        self._mark("crt", main)
         for ev in fp64_in:                    # the own pushes are done before the next step repacks
             main.wait_event(ev)
         if flags:
             await_(_SLOTS - 1)
         else:
             self._barrier()                   # every rank's FP64 pieces have landed
-        return run(2)                         # native path of non-finite rows and columns
+        self._mark("fp64 in", main)
+        run(2)                                # native path of non-finite rows and columns
+        self._mark("end", main)
+        return C
 
     def close(self):
         """Releases plans, packs and, with the residue exchange, the mappings and buffers (call it
