@@ -40,6 +40,8 @@ SIGNATURES = {
     "imd_contract_packed": [_P, C.c_double, C.POINTER(Operand), C.POINTER(Operand), C.c_double,
                             _P, _P, C.c_size_t, _P],
     "imd_wait_flags": [C.POINTER(C.c_void_p), C.c_int, C.c_uint, C.c_uint64, _P],
+    "imd_copy_if_flagged": [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_void_p),
+                            C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32, _P],
 }
 
 

@@ -373,6 +373,29 @@ imd_status_t imd_wait_flags(const unsigned int* const* flags, int num_flags, uns
   return imd::enqueue_wait_flags(flags, num_flags, expect, limit, stream);
 }
 
+/* Copies that run only when a row flag is set (extension; see the header). */
+imd_status_t imd_copy_if_flagged(const unsigned char* const* flags, const int64_t* flag_bytes,
+                                 int32_t num_ranges, void* const* dst, const void* const* src,
+                                 const int64_t* bytes, int32_t num_copies, cudaStream_t stream) {
+  if (num_ranges < 0 || num_ranges > imd::kMaxFlagRanges || num_copies < 0 ||
+      num_copies > imd::kMaxCondCopies)
+    return IMD_STATUS_INVALID_VALUE;
+  if (num_copies == 0) return IMD_STATUS_SUCCESS;
+  if (dst == nullptr || src == nullptr || bytes == nullptr ||
+      (num_ranges > 0 && (flags == nullptr || flag_bytes == nullptr)))
+    return IMD_STATUS_INVALID_VALUE;
+  for (int r = 0; r < num_ranges; ++r)
+    if (flag_bytes[r] < 0 || (flag_bytes[r] > 0 && flags[r] == nullptr)) return IMD_STATUS_INVALID_VALUE;
+  for (int c = 0; c < num_copies; ++c) {
+    if (bytes[c] < 0 || (bytes[c] > 0 && (dst[c] == nullptr || src[c] == nullptr)))
+      return IMD_STATUS_INVALID_VALUE;
+    if (bytes[c] % 8 != 0 || reinterpret_cast<uintptr_t>(dst[c]) % 8 != 0 ||
+        reinterpret_cast<uintptr_t>(src[c]) % 8 != 0)
+      return IMD_STATUS_MISALIGNED;
+  }
+  return imd::enqueue_copy_if_flagged(flags, flag_bytes, num_ranges, dst, src, bytes, num_copies, stream);
+}
+
 /* ---- verification hooks (not part of the drop-in ABI) ---------------------------------------- */
 /* 1: run the slow exact int8 GEMM instead of the tensor-core kernel in later calls (cross-check). */
 IMD_API int imd_test_use_reference_gemm(int on) {

@@ -66,6 +66,13 @@ imd_status_t generate_vectors(const ExecPlan& e, int64_t* vec, cudaStream_t stre
 
 // Bounded wait (one launch of one warp) until every flags[i] (device addresses, n <= kMaxWaitFlags)
 // holds `expect`; gives up after `limit` polls per flag and sets bit 2 of the device error word.
+constexpr int kMaxFlagRanges = 4;
+constexpr int kMaxCondCopies = 16;
+// One launch: copies the ranges src[c] -> dst[c] (8-byte aligned, bytes[c] multiples of 8) only if
+// a byte of the flag ranges is nonzero.
+imd_status_t enqueue_copy_if_flagged(const unsigned char* const* flags, const int64_t* flag_bytes,
+                                     int ranges, void* const* dst, const void* const* src,
+                                     const int64_t* bytes, int copies, cudaStream_t stream);
 constexpr int kMaxWaitFlags = 32;
 imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigned int expect,
                                 unsigned long long limit, cudaStream_t stream);

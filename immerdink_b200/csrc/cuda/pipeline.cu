@@ -1016,6 +1016,58 @@ imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigne
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
 
+// ---- copies that run only when a row is flagged ----------------------------------------------------
+// The native path of non-finite rows is the only reader of a slab's FP64 values. A rank of the
+// multi-GPU driver therefore fetches the other ranks' FP64 pieces only when a row flag of its slabs
+// is set: every CTA scans the (few KB of) flags; if none is set the kernel ends, else the grid
+// copies the ranges with 8-byte loads and stores (sources may be peers' memory).
+namespace {
+
+struct CopyIfParams {
+  const unsigned char* flags[kMaxFlagRanges];
+  long long flag_bytes[kMaxFlagRanges];
+  int ranges;
+  unsigned long long* dst[kMaxCondCopies];
+  const unsigned long long* src[kMaxCondCopies];
+  long long vecs[kMaxCondCopies];   // 8-byte units
+  int copies;
+};
+
+__global__ void __launch_bounds__(kThreads) k_copy_if_flagged(CopyIfParams p) {
+  int mine = 0;
+  for (int r = 0; r < p.ranges; ++r)
+    for (long long i = threadIdx.x; i < p.flag_bytes[r]; i += blockDim.x) mine |= p.flags[r][i];
+  if (!__syncthreads_or(mine)) return;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int c = 0; c < p.copies; ++c)
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.vecs[c];
+         i += step)
+      p.dst[c][i] = p.src[c][i];
+}
+
+}  // namespace
+
+imd_status_t enqueue_copy_if_flagged(const unsigned char* const* flags, const int64_t* flag_bytes,
+                                     int ranges, void* const* dst, const void* const* src,
+                                     const int64_t* bytes, int copies, cudaStream_t stream) {
+  CopyIfParams p = {};
+  p.ranges = ranges, p.copies = copies;
+  for (int r = 0; r < ranges; ++r) p.flags[r] = flags[r], p.flag_bytes[r] = flag_bytes[r];
+  for (int c = 0; c < copies; ++c) {
+    p.dst[c] = static_cast<unsigned long long*>(dst[c]);
+    p.src[c] = static_cast<const unsigned long long*>(src[c]);
+    p.vecs[c] = bytes[c] / 8;
+  }
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
+  k_copy_if_flagged<<<sms * 4, kThreads, 0, stream>>>(p);
+  return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
 // ---- built-in workspace ---------------------------------------------------------------------------
 // A fixed workspace that lives in the library image, for callers that are not in a position to
 // allocate device memory. The name below is only a handle on the host side: its device address is

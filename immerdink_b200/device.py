@@ -77,6 +77,22 @@ def wait_flags(flags, expect, *, max_polls=0, stream=0, lib=None):
         raise _error(st, "imd_wait_flags")
 
 
+def copy_if_flagged(flag_ranges, copies, *, stream=0, lib=None):
+    """imd_copy_if_flagged: enqueue one kernel that performs `copies` = [(dst, src, nbytes), ...]
+    (device addresses, 8-byte granular) only if a byte of `flag_ranges` = [(ptr, nbytes), ...] is
+    nonzero."""
+    lib = load_library(lib)
+    nr, nc = len(flag_ranges), len(copies)
+    fp = (ct.c_void_p * max(nr, 1))(*[int(p) for p, _ in flag_ranges])
+    fb = (ct.c_int64 * max(nr, 1))(*[int(n) for _, n in flag_ranges])
+    dst = (ct.c_void_p * max(nc, 1))(*[int(c[0]) for c in copies])
+    src = (ct.c_void_p * max(nc, 1))(*[int(c[1]) for c in copies])
+    nb = (ct.c_int64 * max(nc, 1))(*[int(c[2]) for c in copies])
+    st = lib.lib.imd_copy_if_flagged(fp, fb, nr, dst, src, nb, nc, stream)
+    if st:
+        raise _error(st, "imd_copy_if_flagged")
+
+
 class Layout(namedtuple("Layout", "shape strides")):
     """Extents and ELEMENT strides of an operand (None = dense), to plan before arrays exist."""
 

@@ -162,13 +162,17 @@ class RankContraction:
     and B, once, for all N moduli, and the pack kernels store the shifts, flags and int8 residue
     planes into its own packed slab buffers (`imd_pack_scatter`: the rows of a piece at their place
     in the slab); copy engines then push those rows into the packed slab buffers of the other
-    consumers of the slab (peers' memory mapped through CUDA IPC, pitched peer-to-peer copies on a
+    consumers of the slab (peers' memory mapped through CUDA IPC, one contiguous peer copy per plane on a
     side stream: no SM is taken from the persistent GEMM), residue group by residue group, so the
     GEMM of one group runs while the planes of the next travel. No rank repeats another's
-    quantisation. The FP64 pieces, which only the native path of non-finite rows reads, travel last:
+    quantisation. The operand whose slab has more consumers is packed first, so that its planes
+    travel while the other is being packed. The FP64 values, which only the native path of
+    non-finite rows reads, do not travel at all in the usual case: every rank stages its pieces in
+    a buffer the others have mapped, and a consumer fetches them (imd_copy_if_flagged, peer loads)
+    only if a row flag of its slabs is set:
 
-        main   barrier | pack own pieces | barrier, GEMM group 0 | barrier, GEMM group 1 | CRT | barrier, native path
-        side                             | push group 0 | push group 1 ...... | push FP64 pieces |
+        main   barrier | pack B | pack A | group 0 in, GEMM 0 | group 1 in, GEMM 1 | CRT | fetch if flagged, native path
+        side           | push B group 0 | push A group 0, B group 1 ... | stage FP64 pieces |
 
     How a consumer learns that a group's planes have landed (`sync`): "barrier" = every rank waits
     for its own copies and the ranks meet in a tiny NCCL all-reduce per group; "flags" = after the
@@ -287,6 +291,7 @@ class RankContraction:
         self.fp64_dests = [[self._owned[2 + x]] for x in (0, 1)]  # gathered FP64 slabs
         self.flags = self._owned[4]                              # [operand][producer position][slot] words
         self.flag_dests = [[], []]                               # the other consumers' flag words
+        self.peer_pos = [[], []]                                 # their positions in the slab
         if part.world == 1:
             return
         # Every rank goes through both collectives whatever fails locally, and all ranks fail together.
@@ -304,9 +309,10 @@ class RankContraction:
         self.dist.all_gather_object(everyone, mine)
         sharers = (part.column_group(), part.row_group())     # ranks that consume the slab of A / B
         for x in (0, 1):
-            for r in sharers[x]:
+            for position, r in enumerate(sharers[x]):
                 if r == part.rank or failure:
                     continue
+                self.peer_pos[x].append(position)
                 for which, out in ((x, self.dests[x]), (2 + x, self.fp64_dests[x]), (4, self.flag_dests[x])):
                     if len(everyone[r][which]) != 64:
                         failure = f"rank {r} exported no handle"
@@ -371,7 +377,7 @@ class RankContraction:
             main.wait_event(b_in)
             return self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
                                       stream=main, packed=(self.packed, None))
-        from .device import wait_flags as _dev_wait
+        from .device import copy_if_flagged as _dev_copy_if, wait_flags as _dev_wait
         rt, s = self._rt, main.cuda_stream
         shards = (shard_a, shard_b)
         kind = rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice
@@ -399,9 +405,9 @@ class RankContraction:
         def word(x, position, slot):          # offset of a flag word inside a rank's flag buffer
             return 4 * ((x * _POSITIONS + position) * _SLOTS + slot)
 
-        def announce(x, j, slot):             # after the copies to consumer j of slab x: its flag word
+        def announce(x, j, slot, on=None):    # after the copies to consumer j of slab x: its flag word
             if flags:
-                copy(j, self.flag_dests[x][j] + word(x, self.pos[x], slot),
+                copy(j if on is None else on, self.flag_dests[x][j] + word(x, self.pos[x], slot),
                      self.values.data_ptr() + 4 * tick, 4)
 
         def await_(slot):                     # every other producer's copies of this slot have landed here
@@ -446,12 +452,15 @@ class RankContraction:
                     announce(x, j, gi)
             arrived.append(None if flags else [st.record_event() for st in pushes])
             self._mark(f"pushed group {gi}", pushes[0])
-        for x in (0, 1):                      # FP64 pieces: only the native path reads them
-            nb = shards[x].numel() * 8
-            for j, dst in enumerate(self.fp64_dests[x][1:]):
-                copy(j, dst + self.pos[x] * nb, shards[x].data_ptr(), nb)
-                announce(x, j, _SLOTS - 1)
-            copy(0, self.fp64_dests[x][0] + self.pos[x] * nb, shards[x].data_ptr(), nb)   # the own buffer
+        # FP64 pieces: only the native path of non-finite rows reads them. Every rank stages its
+        # pieces in its own shared buffer (a local copy, behind the planes) and tells the other
+        # consumers; a consumer fetches them only if a row flag of its slabs is set (below).
+        piece_bytes = [shards[x].numel() * 8 for x in (0, 1)]
+        for x in (0, 1):
+            copy(0, self.fp64_dests[x][0] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(), piece_bytes[x])
+        for x in (0, 1):
+            for j in range(len(self.flag_dests[x])):
+                announce(x, j, _SLOTS - 1, on=0)
         fp64_in = [st.record_event() for st in pushes]
         self._mark("pushed fp64", pushes[0])
         packed = tuple(self.packed)
@@ -481,7 +490,13 @@ class RankContraction:
             await_(_SLOTS - 1)
         else:
             self._barrier()                   # every rank's FP64 pieces have landed
-        self._mark("fp64 in", main)
+        self._mark("fp64 staged", main)
+        fetch = [(self.fp64_dests[x][0] + p * piece_bytes[x], self.fp64_dests[x][1 + j] + p * piece_bytes[x],
+                  piece_bytes[x]) for x in (0, 1) for j, p in enumerate(self.peer_pos[x])]
+        if fetch:                             # the others' FP64 pieces, only if a row of the slabs is flagged
+            rows = [(self.dests[x][0] + self.slab[x].layout["flag"][0],
+                     self.slab[x].layout["b"] * self.slab_rows[x]) for x in (0, 1)]
+            _dev_copy_if(rows, fetch, stream=s, lib=self.lib)
         run(2)                                # native path of non-finite rows and columns
         self._mark("end", main)
         return C

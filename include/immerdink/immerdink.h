@@ -126,6 +126,19 @@ IMD_API imd_status_t imd_pack_scatter(imd_pack_t piece, const double* X, int64_t
 IMD_API imd_status_t imd_wait_flags(const unsigned int* const* flags, int num_flags,
                                     unsigned int expect, uint64_t max_polls, cudaStream_t stream);
 
+/* Copies that run only when a row is flagged (no counterpart in the reference; used by the
+ * multi-GPU driver). The native path of non-finite rows is the only reader of a slab's FP64
+ * values, so a rank fetches the other ranks' FP64 pieces only when a row flag of its packed slabs
+ * is set. Enqueues one kernel on `stream`: if any byte of the num_ranges (0..4) ranges
+ * flags[r][0 .. flag_bytes[r]) is nonzero, the num_copies (0..16) ranges src[c] -> dst[c] of
+ * bytes[c] bytes are copied (sources may be peers' memory mapped into this process); else nothing
+ * is touched. Checks: counts out of range, NULL arrays or NULL pointers of non-empty ranges ->
+ * INVALID_VALUE; dst[c], src[c] or bytes[c] not a multiple of 8 (FP64 data) -> MISALIGNED. */
+IMD_API imd_status_t imd_copy_if_flagged(const unsigned char* const* flags, const int64_t* flag_bytes,
+                                         int32_t num_ranges, void* const* dst,
+                                         const void* const* src, const int64_t* bytes,
+                                         int32_t num_copies, cudaStream_t stream);
+
 /* imd_contract_packed in parts (no counterpart in the reference; used by the multi-GPU driver to
  * start the GEMM of one residue group while the planes of the next are still arriving, and before
  * the FP64 operands of other GPUs have arrived).

@@ -58,3 +58,31 @@ def test_wait_flags_passes_when_set_and_gives_up_when_not():
         device.wait_flags([base] * 33, 7, stream=stream)
     with pytest.raises(imd.MisalignedError):
         device.wait_flags([base + 2], 7, stream=stream)
+
+
+def test_copy_if_flagged_copies_only_when_a_flag_byte_is_set():
+    import torch
+    import immerdink_b200 as imd
+    from immerdink_b200 import device
+    stream = torch.cuda.current_stream().cuda_stream
+    flags = torch.zeros(5000, dtype=torch.uint8, device="cuda")
+    src = torch.arange(3 * 1001, dtype=torch.float64, device="cuda")
+    dst = torch.full_like(src, -1.0)
+    n = 1001 * 8
+    copies = [(dst.data_ptr() + i * n, src.data_ptr() + i * n, n) for i in (0, 2)]
+    ranges = [(flags.data_ptr(), 1234), (flags.data_ptr() + 2000, 3000)]
+    device.copy_if_flagged(ranges, copies, stream=stream)
+    assert bool((dst == -1.0).all())                       # no flag: nothing is touched
+    flags[1500] = 1                                        # outside both ranges
+    device.copy_if_flagged(ranges, copies, stream=stream)
+    assert bool((dst == -1.0).all())
+    flags[4999] = 1                                        # last byte of the second range
+    device.copy_if_flagged(ranges, copies, stream=stream)
+    want = src.clone()
+    want[1001:2002] = -1.0                                 # the piece that was not listed
+    assert torch.equal(dst, want)
+    device.copy_if_flagged(ranges, [], stream=stream)      # nothing to copy
+    with pytest.raises(imd.MisalignedError):
+        device.copy_if_flagged(ranges, [(dst.data_ptr() + 4, src.data_ptr(), 8)], stream=stream)
+    with pytest.raises(imd.InvalidValueError):
+        device.copy_if_flagged(ranges, copies * 9, stream=stream)
