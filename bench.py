@@ -45,6 +45,7 @@ WORKLOADS = {
     "cc1000": ("kjbc,kiac->abij", dict(a=50, b=50, c=50, i=20, j=20, k=20), 14, 7),
 }
 GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}  # ranks over (a, b)
+RANK_GROUP = {2: 4, 4: 4, 8: 3}   # residue group of a rank's plan in the residue exchange, as measured
 SEED = 20251125
 MASK = (1 << 64) - 1
 
@@ -270,10 +271,14 @@ def run_ours(args, rank, world, local_rank):
         shard_a = synth(0, part.shard_shape(0), part.shard_start(0))
         shard_b = synth(1, part.shard_shape(1), part.shard_start(1))
         groups = idist.make_groups(world, dist)
+        # the residue group is also the unit in which planes travel between ranks: smaller groups
+        # start the first GEMM earlier (results do not depend on it)
+        rank_g = args.group or (prob.g if args.exchange == "fp64" else RANK_GROUP.get(world, prob.g))
+        store_push = {"auto": "auto", "none": None, "a": 0, "b": 1}[args.store_push]
         try:
-            rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
+            rankc = idist.RankContraction(part, N=prob.N, g=rank_g, dist=dist, groups=groups,
                                           exchange=args.exchange, push_streams=args.push_streams,
-                                          sync=args.sync)
+                                          sync=args.sync, store_push=store_push)
             ok = torch.ones(1, device=dev)
         except Exception as exc:   # e.g. CUDA IPC closed in this environment
             print(f"rank {rank}: residue exchange unavailable ({exc!r})", file=sys.stderr)
@@ -282,7 +287,7 @@ def run_ours(args, rank, world, local_rank):
         if ok.item() == 0:
             if rankc is not None:
                 rankc.close()
-            rankc = idist.RankContraction(part, N=prob.N, g=prob.g, dist=dist, groups=groups,
+            rankc = idist.RankContraction(part, N=prob.N, g=rank_g, dist=dist, groups=groups,
                                           exchange="fp64")
         A, B, plan, run_spec = rankc.A, rankc.B, rankc.plan, rankc.spec
         Cd = torch.empty(rankc.tile_shape, dtype=torch.float64, device=dev)
@@ -469,9 +474,11 @@ def run_ours(args, rank, world, local_rank):
                                 "" if world == 1 else
                                 "; every step each rank packs its own pieces of A and B once (imd_pack_scatter), "
                                 "copy engines push the residue planes into the other consumers' slab buffers "
-                                "over NVLink group by group while the GEMM of the previous group runs, and the "
-                                "tile is contracted from the packed slabs; FP64 pieces follow for the native "
-                                "path" if rankc.exchange == "residues" else
+                                "over NVLink group by group while the GEMM of the previous group runs (flag "
+                                "words announce them; with three other consumers of one slab the other slab's "
+                                "planes go by the pack kernel's own stores), and the tile is contracted from "
+                                "the packed slabs; FP64 pieces are fetched from peers only when a row is "
+                                "flagged for the native path" if rankc.exchange == "residues" else
                                 "; every step all-gathers the FP64 slabs over NCCL (side stream), packs A "
                                 "while B arrives and contracts the rank's tile")),
                             exchange_alone_ms=exchange_ms, contraction_slabs_resident_ms=resident_ms,
@@ -502,9 +509,12 @@ def run_ours(args, rank, world, local_rank):
     if parity is not None:
         line["parity_sample"] = parity
     if world > 1 and rankc.exchange == "residues":
-        line["config"]["exchange"] = dict(kind="residues", sync=rankc.sync, push_streams=len(rankc.push_streams))
+        line["config"]["exchange"] = dict(kind="residues", sync=rankc.sync, push_streams=len(rankc.push_streams),
+                                          planes_by_pack_kernel_stores=(None if rankc.store_push is None
+                                                                        else "AB"[rankc.store_push]),
+                                          residue_group_per_rank=rank_g)
     elif world > 1:
-        line["config"]["exchange"] = dict(kind="fp64")
+        line["config"]["exchange"] = dict(kind="fp64", residue_group_per_rank=rank_g)
     if world == 1 and not args.no_cpu:
         # DGEMM on the same GPU, same GEMM view
         n = low["m"]
@@ -544,8 +554,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and DGEMM legs")
     ap.add_argument("--slabs", type=int, default=8, help="slabs of the host-operand pipeline (e2e)")
     ap.add_argument("--exchange", default=None, choices=["residues", "fp64"],
-                    help="multi-GPU exchange (default: residues on 2 and 4 GPUs, fp64 on 8)")
-    ap.add_argument("--sync", default="barrier", choices=["barrier", "flags"],
+                    help="multi-GPU exchange (default: residues)")
+    ap.add_argument("--group", type=int, default=0,
+                    help="residue group of the ranks' plans with more than one GPU (0 = as measured best)")
+    ap.add_argument("--store-push", default="auto", choices=["auto", "none", "a", "b"],
+                    help="residue exchange: operand whose planes the pack kernel stores into peers' buffers")
+    ap.add_argument("--sync", default="flags", choices=["barrier", "flags"],
                     help="residue exchange: how consumers learn that planes have landed")
     ap.add_argument("--push-streams", type=int, default=1,
                     help="streams of the residue exchange's peer copies")

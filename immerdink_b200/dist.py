@@ -158,7 +158,7 @@ class RankContraction:
     """One rank's step of the partitioned contraction: exchange + compute, overlapped. Two ways to
     exchange (`exchange`):
 
-    "residues" (the default on 2 and 4 ranks): every rank quantises only ITS pieces of A
+    "residues" (the default with more than one rank): every rank quantises only ITS pieces of A
     and B, once, for all N moduli, and the pack kernels store the shifts, flags and int8 residue
     planes into its own packed slab buffers (`imd_pack_scatter`: the rows of a piece at their place
     in the slab); copy engines then push those rows into the packed slab buffers of the other
@@ -190,7 +190,7 @@ class RankContraction:
     the peers through CUDA IPC (cuda-python)."""
 
     def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
-                 exchange=None, push_streams=1, sync="barrier"):
+                 exchange=None, push_streams=1, sync="flags", store_push="auto"):
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
@@ -202,10 +202,10 @@ class RankContraction:
         self.tile_shape = lc.shape
         nbytes = lambda n: torch.empty(max(int(n), 1), dtype=torch.uint8, device=dev)
         self.side = torch.cuda.Stream(dev)
-        # Defaults as measured (cc8000, whole steps): the residue exchange wins on 4 GPUs (2.48 against
-        # 2.81 ms) and ties on 2; on 8 the copy-engine pushes of one stream to three peers were far
-        # slower (5.2 against 1.79 ms), so 8 ranks exchange FP64.
-        self.exchange = exchange or ("residues" if part.world in (2, 4) else "fp64")
+        # Defaults as measured (cc8000, whole steps): the residue exchange with flag signalling wins on
+        # 2, 4 and 8 GPUs (4.03 against 4.45 ms, and 1.55 against 1.77 ms on 8, where the planes of the
+        # operand with one other consumer go by the pack kernel's own stores).
+        self.exchange = exchange or ("residues" if part.world > 1 else "fp64")
         lays = (la_, lb_, lc)
         specs = [_dev.pack_spec(self.spec, *lays, operand=x, N=N, g=g, rounding=rounding, lib=lib)
                  for x in (0, 1)]
@@ -236,6 +236,20 @@ class RankContraction:
             self._map_peers()
             # copies to different peers may go to different streams (copy engines); one by default
             self.push_streams = [torch.cuda.Stream(dev) for _ in range(max(1, int(push_streams)))]
+            # store_push = the operand (0 = A, 1 = B) whose planes the pack kernel itself stores into the
+            # other consumers' buffers (NVLink stores) instead of the copy engines, or None
+            if store_push == "auto":   # one copy-engine stream carries about 350 GB/s in 8 MB copies: with
+                # three other consumers of one slab, the other slab's planes go by stores
+                store_push = None if max(part.pa, part.pb) < 4 else (0 if part.pa < part.pb else 1)
+            if store_push not in (None, 0, 1):
+                raise ValueError("store_push must be 'auto', None, 0 or 1")
+            self.store_push = store_push
+            # every producer of a slab starts with the consumer after itself and goes round, so that
+            # at any time a consumer receives from one producer (and not all producers send to the
+            # first consumer at once)
+            self.push_order = [sorted(range(len(self.peer_pos[x])),
+                                      key=lambda j, x=x: (self.peer_pos[x][j] - self.pos[x]) %
+                                      (part.pieces_b if x == 0 else part.pieces_a)) for x in (0, 1)]
             self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
             if sync not in ("barrier", "flags"):
                 raise ValueError("sync must be 'barrier' or 'flags'")
@@ -428,7 +442,8 @@ class RankContraction:
                     or shards[x].dtype != torch.float64):
                 raise ValueError("the rank's pieces must be dense FP64 arrays of Partition.shard_shape")
             self.piece[x].scatter_ptr(shards[x].data_ptr(), self.slab_rows[x], self.row0[x],
-                                      self.dests[x][:1], self.slab[x].pack_bytes,
+                                      self.dests[x] if x == self.store_push else self.dests[x][:1],
+                                      self.slab[x].pack_bytes,
                                       self.pack_ws[x].data_ptr(), self.pack_ws[x].numel(), s)
             packed_ev[x] = main.record_event()
             self._mark(f"packed {'AB'[x]}", main)
@@ -443,7 +458,11 @@ class RankContraction:
                 lay, R, b = self.slab[x].layout, self.slab_rows[x], self.slab[x].layout["b"]
                 rp, kh = self.piece[x].layout["r"], lay["k_hat"]
                 own = self.dests[x][0]
-                for j, dst in enumerate(self.dests[x][1:]):
+                for j in self.push_order[x]:
+                    dst = self.dests[x][1 + j]
+                    if x == self.store_push:  # the pack kernel has stored the planes there already
+                        announce(x, j, gi)
+                        continue
                     if gi == 0:
                         copy_rows(j, dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
                         copy_rows(j, dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
