@@ -532,7 +532,7 @@ def run_ours(args, rank, world, local_rank):
         # CPU oracle on a sampled block; the same block checks the GPU result bit for bit
         side = 64
         dt, _, _, _ = cpu_sample(prob, side, side)
-        side = int(max(64, min(1024, side * math.sqrt(12.0 / max(dt, 1e-3)))))
+        side = int(max(64, min(4096, side * math.sqrt(12.0 / max(dt, 1e-3)))))
         dt, fl, out, coff = cpu_sample(prob, side, side)
         got = Cd.reshape(-1)[torch.from_numpy(coff.reshape(-1)).to(dev)].cpu().numpy().reshape(out.shape)
         line["parity_sample"] = dict(outputs=int(out.size),
