@@ -210,7 +210,7 @@ class ClockSampler(threading.Thread):
                           nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
                 if self.recording:
                     self.samples.append(sample)
-                time.sleep(0.001)
+                time.sleep(0.005)   # light: NVML calls take driver locks the copy engines' submissions share
         except Exception as exc:  # NVML missing: report it, never fail the benchmark
             self.error = repr(exc)
         finally:
