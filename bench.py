@@ -351,6 +351,16 @@ def run_ours(args, rank, world, local_rank):
     phases = (C.c_float * 8)()
     lib.lib.imd_prof_read(phases, 8)
     lib.lib.imd_prof_enable(0)
+    step_trace = None
+    if rankc is not None and rankc.exchange == "residues":
+        # one more step with an event at every stage (main and push stream), as a time line of rank 0
+        flush.fill_(0)
+        rankc.trace = []
+        step()
+        barrier()
+        t0 = rankc.trace[0][1]
+        step_trace = {label: round(t0.elapsed_time(e), 3) for label, e in rankc.trace[1:]}
+        rankc.trace = None
     phase_ms = {name: phases[t] / phase_steps for t, name in
                 ((1, "vectors+scale"), (2, "residues"), (3, "gemm"), (4, "crt"), (6, "pack"))}
     t_ms = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -524,6 +534,8 @@ def run_ours(args, rank, world, local_rank):
                               "planes once = 1.34e9 at cc8000)"),
                 device_error=int(err))
     line["host_enqueue_ms_per_step"] = host_ms
+    if step_trace is not None:
+        line["step_trace_ms"] = step_trace
     line["phases_from"] = ("events inside the timed steps" if phases_in_timed_region else
                            f"a separate pass of {phase_steps} steps after the timed ones")
     if parity is not None:
