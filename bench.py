@@ -189,9 +189,10 @@ def run_reference(args, rank):
 class ClockSampler(threading.Thread):
     """SM clock and throttle reasons of one GPU, sampled through NVML while the timed region runs."""
 
-    def __init__(self, index):
+    def __init__(self, index, period=0.005):
         super().__init__(daemon=True)
         self.index, self.samples, self.stop_flag, self.max_mhz = index, [], False, None
+        self.period = period
         self.error = None
         self.ready = threading.Event()     # NVML initialised (its first call takes a while)
         self.recording = False             # samples are kept only inside the timed region
@@ -210,7 +211,7 @@ class ClockSampler(threading.Thread):
                           nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
                 if self.recording:
                     self.samples.append(sample)
-                time.sleep(0.005)   # light: NVML calls take driver locks the copy engines' submissions share
+                time.sleep(self.period)   # light: NVML calls take driver locks that submissions share
         except Exception as exc:  # NVML missing: report it, never fail the benchmark
             self.error = repr(exc)
         finally:
@@ -231,7 +232,8 @@ class ClockSampler(threading.Thread):
         for _, r in self.samples:
             bits |= r
         names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
-                 0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+                 0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+                 0x10: "sync_boost", 0x100: "display_clock_setting"}
         return dict(sm_mhz=sm[len(sm) // 2], sm_min_mhz=sm[0], sm_max_mhz=self.max_mhz,
                     reasons=[n for b, n in names.items() if bits & b], samples=len(self.samples))
 
@@ -312,8 +314,11 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    # rank 0 reports its GPU's clocks; the other ranks do not poll (a step of several GPUs is many
+    # short submissions, which NVML's locks delay)
+    sampler = ClockSampler(local_rank, 0.005 if world == 1 else 0.010)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
@@ -328,7 +333,8 @@ def run_ours(args, rank, world, local_rank):
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(args.steps)]
     barrier()
-    sampler.begin()
+    if rank == 0:
+        sampler.begin()
     host_ms = 0.0
     for s in range(args.steps):
         flush.fill_(s)  # evict the previous step's working set from L2 (outside the timed events)
@@ -338,7 +344,7 @@ def run_ours(args, rank, world, local_rank):
         host_ms += (time.perf_counter() - h0) * 1e3 / args.steps   # enqueue only: nothing waits for the GPU
         ev[s][1].record(stream)
     barrier()
-    clocks = sampler.summary()
+    clocks = sampler.summary() if rank == 0 else None
     ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
     phase_steps = args.steps
     if not phases_in_timed_region:

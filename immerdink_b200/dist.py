@@ -132,6 +132,15 @@ def gather(part, shard_a, shard_b, out_a, out_b, groups, dist):
             dist.all_gather_into_tensor(out.view(-1), shard.contiguous().view(-1), group=grp)
 
 
+def push_order(peer_positions, own_position, sharers):
+    """Order (indices into `peer_positions`) in which the producer at `own_position` of a slab with
+    `sharers` consumers serves the others: the one after itself first, then round. In turn t every
+    producer serves the consumer t + 1 places after it, so no two producers serve one consumer at
+    the same time."""
+    return sorted(range(len(peer_positions)),
+                  key=lambda j: (peer_positions[j] - own_position) % sharers)
+
+
 def piece_pack_spec(part, x, slab_spec):
     """The GIVEN pack spec of a rank's piece of operand x (0 = A, 1 = B): the classes and orders of
     the slab's pack spec (`slab_spec`, of the gathered layout of Partition.plan_layouts) without the
@@ -247,9 +256,8 @@ class RankContraction:
             # every producer of a slab starts with the consumer after itself and goes round, so that
             # at any time a consumer receives from one producer (and not all producers send to the
             # first consumer at once)
-            self.push_order = [sorted(range(len(self.peer_pos[x])),
-                                      key=lambda j, x=x: (self.peer_pos[x][j] - self.pos[x]) %
-                                      (part.pieces_b if x == 0 else part.pieces_a)) for x in (0, 1)]
+            self.push_order = [push_order(self.peer_pos[x], self.pos[x],
+                                          part.pieces_b if x == 0 else part.pieces_a) for x in (0, 1)]
             self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
             if sync not in ("barrier", "flags"):
                 raise ValueError("sync must be 'barrier' or 'flags'")

@@ -143,3 +143,17 @@ def test_pieces_packed_separately_tile_the_slab_pack(world):
                 assert np.array_equal(w, g_), (world, rank, x, l)
             assert np.array_equal(want[sl["sig"][0] + 2 * pos * rp:sl["sig"][0] + 2 * (pos + 1) * rp],
                                   got[pl["sig"][0]:pl["sig"][0] + 2 * rp])
+
+
+def test_push_order_serves_every_consumer_from_one_producer_per_turn():
+    from immerdink_b200.dist import push_order
+    for sharers in (2, 3, 4, 8):
+        turns = {}
+        for own in range(sharers):
+            peers = [p for p in range(sharers) if p != own]
+            order = push_order(peers, own, sharers)
+            assert sorted(order) == list(range(len(peers)))
+            for t, j in enumerate(order):
+                turns.setdefault(t, []).append(peers[j])
+        for t, served in turns.items():
+            assert sorted(served) == list(range(sharers)), (sharers, t, served)
