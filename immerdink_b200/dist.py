@@ -528,6 +528,14 @@ class RankContraction:
         self._mark("end", main)
         return C
 
+    def device_error(self):
+        """Reads and clears the device error word (synchronises the device): nonzero when a
+        bounded wait gave up, e.g. bit 2 (4) when a producer's planes did not arrive within about
+        a second; the step that saw it computed on incomplete slabs and must be repeated."""
+        from .device import load_library
+        lib = getattr(self, "lib", None) or load_library(None)
+        return int(lib.lib.imd_test_device_error()) & 0xFFFFFFFF
+
     def close(self):
         """Releases plans, packs and, with the residue exchange, the mappings and buffers (call it
         on every rank, once no step is in flight anywhere)."""

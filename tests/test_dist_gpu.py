@@ -30,6 +30,7 @@ def test_rank_contraction_world_1_equals_plain_call(exchange):
     imd.contract(spec, A, B, C0, alpha=0.5, N=14, g=7, workspace=ws)
     torch.cuda.synchronize()
     assert same_bits(C1.reshape(C0.shape).cpu().numpy(), C0.cpu().numpy())
+    assert rc.device_error() == 0
     rc.close()
 
 
