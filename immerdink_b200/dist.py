@@ -19,7 +19,7 @@ import math
 from dataclasses import dataclass
 
 GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
-_POSITIONS, _SLOTS = 8, 16      # flag words per operand: producers sharing a slab x (residue groups + FP64)
+_POSITIONS, _SLOTS = 8, 32      # flag words per operand: producers sharing a slab x (residue groups + FP64)
 
 
 @dataclass
@@ -269,6 +269,7 @@ class RankContraction:
             low = self.plan.lowering
             gg, NN = low["residue_group"], low["num_moduli"]
             self.groups_of_planes = [(l0, min(gg, NN - l0)) for l0 in range(0, NN, gg)]
+            assert len(self.groups_of_planes) < _SLOTS, "one flag word per residue group and one for the FP64 pieces"
         self.ws = nbytes(self.plan.workspace_bytes)
 
     # -- set-up of the residue exchange ---------------------------------------------------------
