@@ -152,6 +152,34 @@ inline CrtTables crt_tables(int N) {
   return t;
 }
 
+// Plan-time constants of the FP64 shortcut of the shift rule (dev::fast_shift): the right-hand
+// side as rm 2^re with rm in [rm_lo, rm_hi] (both in [1, 2]), and the factors that turn a
+// floating-point sum of k squares into an enclosure of the exact fixed-point sum S (each of the
+// k additions errs by at most 2^-53 relative, every ceiling adds less than one unit of 2^-60 to
+// a sum that is at least 1).
+struct ShiftFast {
+  double rm_lo, rm_hi;
+  double lo_scale, hi_scale;
+  int32_t re;
+  int32_t usable;  // 0: always take the exact path (k beyond 2^36)
+};
+
+inline ShiftFast shift_fast(const Wide<8>& rhs, uint64_t k) {
+  ShiftFast f{};
+  const int B = wide_bitlen(rhs);
+  if (B < 54 || k > (uint64_t{1} << 36)) return f;
+  const Wide<8> top = wide_shr(rhs, B - 53);
+  const uint64_t mant = top.w[0] | (static_cast<uint64_t>(top.w[1]) << 32);  // 2^52 <= mant < 2^53
+  f.rm_lo = static_cast<double>(mant) * 0x1p-52;
+  f.rm_hi = static_cast<double>(mant + 1) * 0x1p-52;
+  f.re = B - 1;
+  const double kd = static_cast<double>(k);
+  f.lo_scale = 1.0 - (kd + 512.0) * 0x1p-51;
+  f.hi_scale = 1.0 + (kd + 512.0) * 0x1p-51 + (kd + 1.0) * 0x1p-59;
+  f.usable = 1;
+  return f;
+}
+
 inline uint64_t ceil_sqrt_u64(uint64_t k) {
   if (k == 0) return 0;
   uint64_t lo = 0, hi = uint64_t{1} << 32;  // smallest r with r * r >= k

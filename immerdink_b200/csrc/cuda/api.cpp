@@ -418,6 +418,11 @@ IMD_API int imd_test_gemm_l2_hints(int on) {
   if (on >= 0) imd::gemm_l2_hints() = on;
   return imd::gemm_l2_hints();
 }
+/* 1: later calls compute every shift from the exact 128-bit sum of squares (no FP64 shortcut). */
+IMD_API int imd_test_force_exact_shift(int on) {
+  imd::force_exact_shift() = on != 0;
+  return 0;
+}
 IMD_API int imd_test_gemm_variant(int v) {
   imd::gemm_variant() = v;
   return 0;

@@ -22,6 +22,7 @@
 
 #include <cuda.h>
 
+#include "common/modred.hpp"
 #include "kernels.hpp"
 
 namespace imd {
@@ -193,11 +194,7 @@ __device__ __forceinline__ uint4 reduce16(const uint32_t* acc, uint4 prev, bool 
     uint32_t word = 0;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const uint32_t u = acc[4 * wd + b] + bias;       // in [0, 2^32): |acc| < 2^31 - 2^20
-      uint32_t r = u - __umulhi(u, magic) * p;         // in [0, 2 p)
-      r = min(r, r - p);                               // unsigned wrap: r - p is huge when r < p
-      const uint32_t v = r * q;                        // < 2^16
-      uint32_t y = v - __umulhi(v, magic_up) * p;      // (q r) mod p, exact
+      uint32_t y = mod_epilogue(acc[4 * wd + b], p, magic, magic_up, bias, q);  // (q acc) mod p
       if (add) {
         y += (pv[wd] >> (8 * b)) & 0xFFu;              // both < p
         y = min(y, y - p);
@@ -492,12 +489,14 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // every tcgen05 instruction of this kernel names cta_group::2; the allocation is made by one
+  // warp of each CTA of the pair, which gives both the same columns
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(kTmemCols)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   cluster_sync_all();
@@ -506,12 +505,18 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int64_t total = static_cast<int64_t>(p.s.planes) * p.tiles_m * p.tiles_n;
   const int64_t first = blockIdx.x >> 1, step = gridDim.x >> 1;
+  // a role that gives up also raises the other CTA's abort flag, so that both leave promptly
+  const uint32_t peer_abort = map_to_cta(smem_u32(const_cast<int*>(abort)), rank ^ 1u);
+  auto tell_peer = [&]() {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_abort), "r"(1u) : "memory");
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t issued = 0;  // bit s: a load into stage s is (or was) in flight
       bool okay = true;
       const uint64_t pol_a = l2_policy(p.l2_hints & 3), pol_b = l2_policy((p.l2_hints >> 2) & 3);
       for (int64_t w = first; w < total && okay; w += step) {
@@ -519,6 +524,7 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty(stage), phase ^ 1u, abort)) {
             okay = false;
+            tell_peer();
             break;
           }
           const uint32_t leader_full = map_to_cta(full(stage), 0);
@@ -529,11 +535,20 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                            c.plane, pol_a);
           tma_load_3d_pair(dst + kBytesA, &map_b, leader_full, kx,
                            c.tn * 256 + static_cast<int>(rank) * 128, c.plane, pol_b);
+          issued |= 1u << stage;
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
+      }
+      if (!okay && leader) {
+        // give the copies of both CTAs still in flight a bounded time to land (they complete on
+        // the leader's barriers) before the pair passes its final cluster barrier and exits
+        for (int s = 0; s < kPairStages; ++s)
+          if (issued & (1u << s))
+            for (uint32_t it = 0; it < (1u << 20); ++it)
+              if (mbar_try_wait(full(s), 0) || mbar_try_wait(full(s), 1)) break;
       }
     }
   } else if (warp == 1) {
@@ -543,12 +558,16 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t phase = 0, acc_phase = 0;
       bool okay = true;
       for (int64_t w = first; w < total && okay; w += step) {
-        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort)) break;
+        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort)) {
+          tell_peer();
+          break;
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccCols;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(full(stage), phase, abort)) {
             okay = false;
+            tell_peer();
             break;
           }
           tc_fence_after();
@@ -579,7 +598,10 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t acc_phase = 0;
     for (int64_t w = first; w < total; w += step) {
       const TileCoord c = pair_tile_of(p, w);
-      if (!mbar_wait(tfull(acc), acc_phase, abort)) break;
+      if (!mbar_wait(tfull(acc), acc_phase, abort)) {
+        if (lane == 0) tell_peer();
+        break;
+      }
       tc_fence_after();
       const int slot = c.plane / p.s.batches, lam = c.plane % p.s.batches;
       const uint32_t pm = p.s.p[slot], magic = p.s.magic[slot], bias = p.s.bias[slot];
@@ -619,7 +641,7 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0 && *abort) atomicOr(p.error_word, 2u);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(kTmemCols)
                  : "memory");
   }
@@ -628,8 +650,10 @@ k_gemm_i8_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---- tensor-pipe probe ---------------------------------------------------------------------------
 // Issues tcgen05.mma.kind::i8 back to back on whatever the shared memory holds (no loads, results
 // discarded): the time gives the ceiling of the int8 tensor pipe for the tile shapes used above,
-// the denominator of the GEMM roofline. pair = 0: M128 N256 per CTA; pair = 1: M256 N256 per CTA pair.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64, 1) k_mma_probe(int iters, int pair) {
+// the denominator of the GEMM roofline. PAIR = false: M128 N256 per CTA; PAIR = true: M256 N256
+// per CTA pair (every tcgen05 instruction of an instantiation names one cta_group).
+template <bool PAIR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64, 1) k_mma_probe(int iters) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -641,25 +665,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64, 1) k_mma_probe(i
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (threadIdx.x < 32) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&tmem_slot)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&tmem_slot)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&tmem_slot)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  if (threadIdx.x == 0 && (!pair || rank == 0)) {
+  if (threadIdx.x == 0 && (!PAIR || rank == 0)) {
     uint32_t phase = 0;
     for (int it = 0; it < iters; it += 64) {
       for (int j = 0; j < 64; ++j) {
         const uint32_t a = tiles + (j & 3) * kMmaK, b = tiles + kBytesA + (j & 3) * kMmaK;
-        if (pair) tc_mma_i8_pair(tmem_base + (j & 1) * kAccCols, smem_desc(a), smem_desc(b), kPairInstrDesc, 1u);
+        if (PAIR) tc_mma_i8_pair(tmem_base + (j & 1) * kAccCols, smem_desc(a), smem_desc(b), kPairInstrDesc, 1u);
         else tc_mma_i8(tmem_base + (j & 1) * kAccCols, smem_desc(a), smem_desc(b), kInstrDesc, 1u);
       }
-      if (pair) tc_commit_pair(smem_u32(&bar), 1);
+      if (PAIR) tc_commit_pair(smem_u32(&bar), 1);
       else tc_commit(smem_u32(&bar));
       for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
         if (mbar_try_wait(smem_u32(&bar), phase)) break;
@@ -670,9 +702,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64, 1) k_mma_probe(i
   cluster_sync_all();
   if (threadIdx.x < 32) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(kTmemCols)
-                 : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(kTmemCols)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(kTmemCols)
+                   : "memory");
   }
 }
 
@@ -764,15 +801,18 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
 // int8 ops per second of the bare tensor pipe (see k_mma_probe); 0 on failure. Synchronises.
 double mma_probe_tops(int pair, int sms) {
   const int smem = kBytesA + kBytesB + 2048;
-  if (cudaFuncSetAttribute(k_mma_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(k_mma_probe<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+      cudaFuncSetAttribute(k_mma_probe<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return 0.0;
   const int iters = 64 * 256;
   const int grid = sms / 2 * 2;
   cudaEvent_t e0, e1;
   if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return 0.0;
-  k_mma_probe<<<grid, 64, smem>>>(64, pair);  // warm-up
+  if (pair) k_mma_probe<true><<<grid, 64, smem>>>(64);  // warm-up
+  else k_mma_probe<false><<<grid, 64, smem>>>(64);
   cudaEventRecord(e0);
-  k_mma_probe<<<grid, 64, smem>>>(iters, pair);
+  if (pair) k_mma_probe<true><<<grid, 64, smem>>>(iters);
+  else k_mma_probe<false><<<grid, 64, smem>>>(iters);
   cudaEventRecord(e1);
   float ms = 0;
   const bool ok = cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;

@@ -79,6 +79,9 @@ imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigne
 
 // Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.
 bool& use_reference_gemm();
+// Verification switch: 1 = the scale step never takes its FP64 shortcut (every row's shift comes
+// from the exact 128-bit sum), so that both ways can be compared on the same rows.
+int& force_exact_shift();
 // Verification switch for the tensor-core kernel: 0 = chosen by shape, 1 = one CTA per 128 x 256
 // tile, 2 = CTA pairs on 256 x 256 tiles.
 int& gemm_variant();

@@ -9,6 +9,7 @@
 #include <cstdint>
 
 #include "carry.cuh"
+#include "common/modred.hpp"
 #include "common/wide.hpp"
 #include "kernels.hpp"
 
@@ -81,6 +82,27 @@ __device__ inline int shift_from_sum(uint64_t S_hi, uint64_t S_lo, int lhs_shift
   return u - gamma;
 }
 
+// The shift from one floating-point pass over a row. mx = the largest high word of |a_h| (sign
+// cleared), acc = the FP64 sum of the squares a_h^2 in any order. With gamma = ilogb of the
+// largest entry, S 2^(2 gamma - 60) lies in [acc lo_scale, acc hi_scale] (see ShiftFast), so
+// t = rhs / (S << lhs_shift) is enclosed by two directed divisions; u = floor(log4 t) is decided
+// when both ends agree. Rows with a non-finite entry, without a normal entry, or with
+// |gamma| > 400 (squares could leave the normal range) are left to the exact integer path.
+__device__ __forceinline__ bool fast_shift(uint32_t mx, double acc, const ShiftFast& c,
+                                           int lhs_shift, int* sigma) {
+  const int ef = static_cast<int>(mx >> 20);
+  if (!c.usable || ef < 1023 - 400 || ef > 1023 + 400 || !(acc > 0.0)) return false;
+  const int gamma = ef - 1023;
+  const double lo = __dmul_rd(acc, c.lo_scale), hi = __dmul_ru(acc, c.hi_scale);
+  const double t_lo = __ddiv_rd(c.rm_lo, hi), t_hi = __ddiv_ru(c.rm_hi, lo);
+  const int E = c.re - kFracBits + 2 * gamma - lhs_shift;
+  const int e_lo = (static_cast<int>(__double_as_longlong(t_lo) >> 52) & 0x7FF) - 1023 + E;
+  const int e_hi = (static_cast<int>(__double_as_longlong(t_hi) >> 52) & 0x7FF) - 1023 + E;
+  if ((e_lo >> 1) != (e_hi >> 1)) return false;
+  *sigma = (e_lo >> 1) - gamma;
+  return true;
+}
+
 // |a'| = RN_even(|a| 2^sigma) (or truncation) as a 96-bit integer (lo, hi); neg = sign of a'.
 __device__ __forceinline__ void quantize(uint64_t bits, int sigma, bool trunc, uint64_t* lo,
                                          uint32_t* hi, bool* neg) {
@@ -131,10 +153,7 @@ __device__ __forceinline__ int64_t quantize_i64(uint64_t bits, int sigma, bool t
 // Signed base-256 digits of a two's complement integer: adding 0x80 to every byte but the top one
 // (with carries) and flipping those bits back turns each byte into a digit in [-128, 127].
 __device__ __forceinline__ void signed_digits64(int64_t x, uint32_t* d0, uint32_t* d1) {
-  const uint64_t k = 0x0080808080808080ull;
-  const uint64_t y = (static_cast<uint64_t>(x) + k) ^ k;
-  *d0 = static_cast<uint32_t>(y);
-  *d1 = static_cast<uint32_t>(y >> 32);
+  imd::signed_digits64(x, d0, d1);
 }
 __device__ __forceinline__ void signed_digits96(uint64_t lo, uint32_t hi, bool neg, uint32_t* d0,
                                                 uint32_t* d1, uint32_t* d2) {
@@ -166,6 +185,8 @@ __device__ __forceinline__ uint32_t symmetric4(const ResidueTables& t, int l, ui
   const uint32_t above = ((packed + t.fix_add[l]) >> 7) & 0x01010101u;  // 1 where u > ceil(p/2) - 1
   return above * t.fix_mul[l] + packed;                                 // u + 256 - p there
 }
+
+using imd::reduce_sym;
 
 // ---- CRT ------------------------------------------------------------------------------------
 // z = centred representative of the residues, as sign + magnitude on WORDS 32-bit words.

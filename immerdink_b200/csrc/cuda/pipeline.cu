@@ -19,6 +19,7 @@
 
 #include "kernels.hpp"
 #include "numerics.cuh"
+#include "quantize.cuh"
 
 namespace imd {
 
@@ -27,7 +28,6 @@ namespace {
 __device__ unsigned int g_error_word = 0;
 
 constexpr int kThreads = 256;
-constexpr int kMaxDests = 8;  // buffers one pack launch can write (the consumers of a slab)
 
 // ---- scatter vectors -------------------------------------------------------------------------
 struct VecParams {
@@ -84,10 +84,12 @@ Vectors split_vectors(const int64_t* v, const ExecPlan& e) {
   return r;
 }
 
-// ---- scale -----------------------------------------------------------------------------------
+// ---- scale (launches of its own: operands that are contiguous along their rows) -------------------
 // A CTA owns 2^lg_rt rows completely (a row's shift is produced and consumed inside one CTA);
 // its 256 threads are 2^lg_rt rows x KT lanes along K. `rows_fast` picks which of the two runs
 // along consecutive threads, so that global loads coalesce along the operand's fast direction.
+// One pass over the row gives the flag, the largest exponent and the FP64 sum of squares that
+// decides the shift (dev::fast_shift); rows it cannot decide redo the sum with exact integers.
 struct ScaleParams {
   const double* X;
   const int64_t *row, *kv, *bat;
@@ -95,7 +97,9 @@ struct ScaleParams {
   int32_t lg_rt;
   int32_t rows_fast;
   int32_t lhs_shift;
+  int32_t force_exact;
   Wide<8> rhs;
+  ShiftFast fast;
   // Outputs: row i of batch lambda at index lambda * out_rows + out_row0 + i of every destination
   // (one destination and out_rows = rows, out_row0 = 0 inside a contraction; several, possibly
   // in other GPUs' memory, when a piece of a slab is packed for all its consumers).
@@ -106,7 +110,7 @@ struct ScaleParams {
 };
 
 __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ ScaleParams p) {
-  __shared__ int s_gamma[kThreads];
+  __shared__ uint32_t s_max[kThreads];
   __shared__ uint64_t s_hi[kThreads], s_lo[kThreads];
   const int RT = 1 << p.lg_rt, KT = kThreads >> p.lg_rt;
   const int tid = threadIdx.x;
@@ -118,9 +122,9 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
   const double* base = p.X;
   if (live) base += p.bat[rho / p.rows] + p.row[rho % p.rows];
 
-  // pass 1: non-finite flag and largest exponent. Encoding: bit 30 = flag; low bits = gamma + 2048
-  // (0 = no finite nonzero entry).
-  int g = 0;
+  // the pass: largest high word of |a| (exponent and non-finite test in one) and sum of squares
+  uint32_t mx = 0;
+  double acc = 0.0;
   if (live)
     for (int64_t h = kl; h < p.k; h += 4 * KT) {
       uint64_t u[4];
@@ -131,96 +135,53 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int ef = static_cast<int>(u[j] >> 52) & 0x7FF;
-        if (ef == 0x7FF) {
-          g |= 1 << 30;
-        } else if (ef != 0) {
-          g = (g & (1 << 30)) | max(g & 0xFFFF, ef + 1025);  // E + 52 + 2048 with E = ef - 1075
-        } else if ((u[j] << 1) != 0) {                       // subnormal: true exponent
-          uint64_t M;
-          int E;
-          dev::decompose(u[j], &M, &E);
-          g = (g & (1 << 30)) | max(g & 0xFFFF, E + 52 + 2048);
-        }
+        mx = max(mx, static_cast<uint32_t>(u[j] >> 32) & 0x7FFFFFFFu);
+        const double x = __longlong_as_double(static_cast<long long>(u[j]));
+        acc = __fma_rn(x, x, acc);
       }
     }
   const int slot = r * KT + kl;
-  s_gamma[slot] = g;
-  __syncthreads();
-  for (int s = KT >> 1; s > 0; s >>= 1) {
-    if (kl < s) {
-      const int a = s_gamma[slot], b = s_gamma[slot + s];
-      s_gamma[slot] = ((a | b) & (1 << 30)) | max(a & 0xFFFF, b & 0xFFFF);
-    }
-    __syncthreads();
-  }
-  const int gf = s_gamma[r * KT];
-  const bool any = (gf & 0xFFFF) != 0;
-  const int gamma = (gf & 0xFFFF) - 2048;
-
-  // pass 2, fast: an FP64 sum of squares of x = a 2^-gamma encloses the exact S (each ceil adds
-  // less than 1; k fused multiply-adds of positive terms err by at most (k + 512) 2^-52 relative,
-  // taken twice over). If both ends of the enclosure give the same shift, that is the shift.
-  double acc = 0.0;
-  if (live && any)
-    for (int64_t h = kl; h < p.k; h += 4 * KT) {
-      uint64_t u[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int64_t hj = h + static_cast<int64_t>(j) * KT;
-        u[j] = hj < p.k ? static_cast<uint64_t>(__double_as_longlong(base[p.kv[hj]])) : 0ull;
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int ef = static_cast<int>(u[j] >> 52) & 0x7FF;
-        const int xe = ef - gamma;  // exponent field of x; <= 0: x^2 is far below the enclosure width
-        if (ef != 0 && ef != 0x7FF && xe > 0) {
-          const double x = __longlong_as_double(static_cast<long long>(
-              (u[j] & 0x000FFFFFFFFFFFFFull) | (static_cast<uint64_t>(xe) << 52)));
-          acc = __fma_rn(x, x, acc);
-        }
-      }
-    }
   double* s_acc = reinterpret_cast<double*>(s_hi);
+  s_max[slot] = mx;
   s_acc[slot] = acc;
   __syncthreads();
   for (int s = KT >> 1; s > 0; s >>= 1) {
-    if (kl < s) s_acc[slot] += s_acc[slot + s];
+    if (kl < s) {
+      s_max[slot] = max(s_max[slot], s_max[slot + s]);
+      s_acc[slot] += s_acc[slot + s];
+    }
     __syncthreads();
   }
-  int sg = 0;
-  int exact = 0;
-  if (live && kl == 0 && any) {
-    const double sum = s_acc[slot];
-    const double eps = (static_cast<double>(p.k) + 512.0) * 0x1p-51;
-    // the enclosure needs a normal gamma, a sane k and a sum that saw the largest entry
-    if (gamma < -900 || p.k > (int64_t{1} << 36) || !(sum >= 0.99)) {
-      exact = 1;
-    } else {
-      const double lo_d = sum - sum * eps, hi_d = sum + sum * eps;
-      // d 2^60 as a 128-bit integer: floor for the lower end, ceil + k + 1 for the upper end
-      auto to_u128 = [](double d, bool up, uint64_t* h, uint64_t* l) {
-        const uint64_t bits = static_cast<uint64_t>(__double_as_longlong(d));
-        const uint64_t m = (bits & 0x000FFFFFFFFFFFFFull) | (1ull << 52);
-        const int sh = static_cast<int>(bits >> 52) - 1023 - 52 + kFracBits;  // >= 7 as d >= 0.98
-        *l = sh >= 64 ? 0 : m << sh;
-        *h = sh >= 64 ? m << (sh - 64) : (sh == 0 ? 0 : m >> (64 - sh));
-        (void)up;
-      };
-      uint64_t lh, ll, hh, hl;
-      to_u128(lo_d, false, &lh, &ll);
-      to_u128(hi_d, true, &hh, &hl);
-      const uint64_t add = static_cast<uint64_t>(p.k) + 1;
-      hl += add;
-      hh += hl < add ? 1 : 0;
-      const int s_small = dev::shift_from_sum(hh, hl, p.lhs_shift, p.rhs, gamma);  // largest S
-      const int s_large = dev::shift_from_sum(lh, ll, p.lhs_shift, p.rhs, gamma);  // smallest S
-      sg = s_small;
-      exact = s_small != s_large;
-    }
-  }
-  // exact integer pass, for every row of the CTA, when any of its rows could not be decided
+  int sg = 0, fl = 0, exact = 0;
+  if (live && kl == 0)
+    if (p.force_exact || !dev::fast_shift(s_max[slot], s_acc[slot], p.fast, p.lhs_shift, &sg)) exact = 1;
+
+  // exact integer passes, for every row of the CTA, when any of its rows could not be decided
   if (__syncthreads_or(exact)) {
+    // non-finite flag and largest exponent. Encoding: bit 30 = flag; low bits = gamma + 2048
+    // (0 = no finite nonzero entry).
+    int g = 0;
+    if (live)
+      for (int64_t h = kl; h < p.k; h += KT) {
+        uint64_t M;
+        int E;
+        const int kind = dev::decompose(static_cast<uint64_t>(__double_as_longlong(base[p.kv[h]])), &M, &E);
+        if (kind < 0) g |= 1 << 30;
+        else if (kind > 0) g = (g & (1 << 30)) | max(g & 0xFFFF, E + 52 + 2048);
+      }
+    s_max[slot] = static_cast<uint32_t>(g);
+    __syncthreads();
+    for (int s = KT >> 1; s > 0; s >>= 1) {
+      if (kl < s) {
+        const int a = static_cast<int>(s_max[slot]), b = static_cast<int>(s_max[slot + s]);
+        s_max[slot] = static_cast<uint32_t>(((a | b) & (1 << 30)) | max(a & 0xFFFF, b & 0xFFFF));
+      }
+      __syncthreads();
+    }
+    const int gf = static_cast<int>(s_max[r * KT]);
+    const bool any = (gf & 0xFFFF) != 0;
+    const int gamma = (gf & 0xFFFF) - 2048;
+    __syncthreads();  // s_hi doubles as the sum of squares above: every read of it is done
     uint64_t hi = 0, lo = 0;
     if (live && any)
       for (int64_t h = kl; h < p.k; h += KT) {
@@ -246,127 +207,17 @@ __global__ void __launch_bounds__(kThreads) k_scale(const __grid_constant__ Scal
       }
       __syncthreads();
     }
+    sg = 0;
     if (live && kl == 0 && any)
       sg = dev::shift_from_sum(s_hi[slot], s_lo[slot], p.lhs_shift, p.rhs, gamma);
+    fl = (gf >> 30) & 1;
   }
   if (live && kl == 0) {
     const int64_t lam = rho / p.rows;
     const int64_t at = lam * p.out_rows + p.out_row0 + (rho - lam * p.rows);
     for (int dst = 0; dst < p.n_out; ++dst) {
       p.sigma[dst][at] = static_cast<int16_t>(sg);
-      p.flag[dst][at] = (gf >> 30) & 1;
-    }
-  }
-}
-
-// ---- residues --------------------------------------------------------------------------------
-// One thread = 16 consecutive K positions of one row: gather, quantise, emit the group's moduli as
-// 16-byte stores into K-contiguous int8 planes R[slot][batch][rows_pad][k_hat]. Rows >= rows (the
-// padding up to rows_pad) and positions >= k (the padding up to k_hat) are written as zeros, so
-// every byte the GEMM reads is written by this call.
-struct ResidueParams {
-  const double* X;
-  const int64_t *row, *kv, *bat;
-  int64_t rows, rows_pad, batches, k, k_hat;
-  // Output rows: a batch's planes have plane_rows rows, the rows of this launch start at row0
-  // (plane_rows = rows_pad, row0 = 0 inside a contraction); sigma has sigma_rows rows per batch
-  // (rows inside a contraction, plane_rows in a packed buffer) and the same row0.
-  int64_t plane_rows, row0, sigma_rows;
-  int64_t k_run;       // length of the runs of K positions that are adjacent in memory (0: none)
-  int32_t rows_fast;
-  int32_t lg_fast;     // log2 of the threads of a CTA that run along the fast direction
-  int32_t trunc;
-  int32_t mod0, mods;  // first modulus and number of moduli of the group
-  const int16_t* sigma;
-  int32_t n_out;
-  int8_t* R[kMaxDests];
-  ResidueTables t;
-};
-
-// Grid: x covers the fast direction of the operand (K chunks when K is contiguous, rows when the
-// rows are) with 2^lg_fast threads of each CTA, y (and the remaining threads) stride over the other
-// one, so no thread divides a 64-bit index.
-template <int WORDS>
-__global__ void __launch_bounds__(kThreads) k_residues(const __grid_constant__ ResidueParams p) {
-  const int64_t chunks = p.k_hat >> 4;
-  const int64_t total_rows = p.rows_pad * p.batches;
-  const int F = 1 << p.lg_fast, per = kThreads >> p.lg_fast;
-  const int64_t fast = static_cast<int64_t>(blockIdx.x) * F + (threadIdx.x & (F - 1));
-  const int64_t fast_n = p.rows_fast ? total_rows : chunks;
-  const int64_t slow_n = p.rows_fast ? chunks : total_rows;
-  if (fast >= fast_n) return;
-  const int64_t plane = p.batches * p.plane_rows * p.k_hat;
-  for (int64_t slow = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
-       slow < slow_n; slow += static_cast<int64_t>(gridDim.y) * per) {
-    const int64_t rho = p.rows_fast ? fast : slow;
-    const int64_t c = p.rows_fast ? slow : fast;
-    int64_t lam = 0, i = rho;
-    if (p.batches != 1) {
-      lam = rho / p.rows_pad;
-      i = rho - lam * p.rows_pad;
-    }
-    const bool live = i < p.rows;
-    uint32_t d0[16], d1[16], d2[16];
-    const int64_t h0 = c << 4;
-    if (live) {
-      const double* base = p.X + p.bat[lam] + p.row[i];
-      const int sg = p.sigma[lam * p.sigma_rows + p.row0 + i];
-      // all sixteen loads are issued before anything is computed
-      uint64_t raw[16];
-      bool run = false;
-      if (p.k_run >= 16 && h0 + 16 <= p.k) {
-        const int64_t r0 = p.k_run >= p.k ? h0 : h0 % p.k_run;
-        run = r0 + 16 <= p.k_run;  // the sixteen positions are adjacent in memory
-      }
-      if (run) {
-        const double* src = base + p.kv[h0];
-        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-          const ulonglong2* v = reinterpret_cast<const ulonglong2*>(src);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const ulonglong2 t = v[e];
-            raw[2 * e] = t.x;
-            raw[2 * e + 1] = t.y;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) raw[e] = static_cast<uint64_t>(__double_as_longlong(src[e]));
-        }
-      } else {
-        int64_t idx[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) idx[e] = h0 + e < p.k ? p.kv[h0 + e] : -1;
-#pragma unroll
-        for (int e = 0; e < 16; ++e)
-          raw[e] = h0 + e < p.k ? static_cast<uint64_t>(__double_as_longlong(base[idx[e]])) : 0ull;
-      }
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        if (WORDS == 2) {
-          dev::signed_digits64(dev::quantize_i64(raw[e], sg, p.trunc != 0), &d0[e], &d1[e]);
-          d2[e] = 0;
-        } else {
-          uint64_t lo;
-          uint32_t hi;
-          bool neg;
-          dev::quantize(raw[e], sg, p.trunc != 0, &lo, &hi, &neg);
-          dev::signed_digits96(lo, hi, neg, &d0[e], &d1[e], &d2[e]);
-        }
-      }
-    }
-    const int64_t out = (lam * p.plane_rows + p.row0 + i) * p.k_hat + h0;
-    for (int s = 0; s < p.mods; ++s) {
-      uint32_t pk[4] = {0, 0, 0, 0};
-      if (live) {
-        const int l = p.mod0 + s;
-#pragma unroll
-        for (int e = 0; e < 16; ++e)
-          pk[e >> 2] |= dev::residue_u<WORDS>(p.t, l, d0[e], d1[e], d2[e]) << (8 * (e & 3));
-#pragma unroll
-        for (int wd = 0; wd < 4; ++wd) pk[wd] = dev::symmetric4(p.t, l, pk[wd]);
-      }
-      for (int dst = 0; dst < p.n_out; ++dst)
-        *reinterpret_cast<uint4*>(p.R[dst] + out + s * plane) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      p.flag[dst][at] = static_cast<uint8_t>(fl);
     }
   }
 }
@@ -622,6 +473,11 @@ bool& use_reference_gemm() {
   return v;
 }
 
+int& force_exact_shift() {
+  static int v = 0;  // verification hook only
+  return v;
+}
+
 // Phase timing for the benchmark: when enabled, enqueue_contract records an event from a
 // preallocated pool on the caller's stream at every phase boundary. Off by default; one caller
 // at a time (the pool is process-global).
@@ -715,7 +571,9 @@ bool launch_scale(const ExecPlan& e, const OperandView& o, const PackDests& d, c
   p.rows_fast = o.rows_fast;
   p.lg_rt = scale_lg_rt(o.rows_fast, e.k, o.rows * e.b);
   p.lhs_shift = e.lhs_shift;
+  p.force_exact = force_exact_shift();
   p.rhs = e.rhs;
+  p.fast = e.fast;
   p.out_rows = o.out_rows > 0 ? o.out_rows : o.rows;
   p.out_row0 = o.out_row0;
   p.n_out = d.n;
@@ -726,10 +584,16 @@ bool launch_scale(const ExecPlan& e, const OperandView& o, const PackDests& d, c
   return launched();
 }
 
-// Residue planes of moduli [mod0, mod0 + mods) of one operand into R[slot][batch][rows_pad][k_hat].
-bool launch_residues(const ExecPlan& e, const ResidueTables& t, const OperandView& o,
-                     const PackDests& d, int mod0, int mods, cudaStream_t stream) {
-  ResidueParams p{};
+// An operand whose K direction is the contiguous one is quantised by fused launches (shift and
+// residues of the first group in one kernel, the row read from HBM once); one that is contiguous
+// along its rows gets its shifts from k_scale first, and tiles of 8 adjacent rows afterwards.
+bool fuses(const OperandView& o) { return !o.rows_fast; }
+
+// Residue planes of moduli [mod0, mod0 + mods) of one operand into R[slot][batch][rows_pad][k_hat];
+// with `fused` also the operand's shifts and flags (into every destination).
+bool launch_quantize(const ExecPlan& e, const ResidueTables& t, const OperandView& o,
+                     const PackDests& d, int mod0, int mods, bool fused, cudaStream_t stream) {
+  QuantParams p{};
   p.X = o.X;
   p.row = o.row, p.kv = o.kv, p.bat = o.bat;
   p.rows = o.rows;
@@ -737,29 +601,49 @@ bool launch_residues(const ExecPlan& e, const ResidueTables& t, const OperandVie
   p.batches = e.b;
   p.k = e.k;
   p.k_hat = e.k_hat;
-  p.rows_fast = o.rows_fast;
-  p.k_run = o.k_run;
+  p.contig = o.k_run >= e.k ? 2 : (o.k_run >= 8 ? 1 : 0);
   p.trunc = e.trunc;
   p.mod0 = mod0;
   p.mods = mods;
+  p.force_exact = force_exact_shift();
+  p.lhs_shift = e.lhs_shift;
+  p.rhs = e.rhs;
+  p.fast = e.fast;
   const bool placed = o.out_rows > 0;  // rows of a larger packed buffer
   p.plane_rows = placed ? o.out_rows : o.rows_pad;
   p.sigma_rows = placed ? o.out_rows : o.rows;
   p.row0 = o.out_row0;
-  p.sigma = d.sigma[0];
+  p.sigma_in = d.sigma[0];
+  p.flag_in = d.flag[0];
   p.n_out = d.n;
-  for (int i = 0; i < d.n; ++i) p.R[i] = d.res[i];
+  for (int i = 0; i < d.n; ++i) p.sigma[i] = d.sigma[i], p.flag[i] = d.flag[i], p.R[i] = d.res[i];
   p.t = t;
-  const int64_t fast_n = p.rows_fast ? p.rows_pad * p.batches : (p.k_hat >> 4);
-  const int64_t slow_n = p.rows_fast ? (p.k_hat >> 4) : p.rows_pad * p.batches;
-  p.lg_fast = 0;
-  while (p.lg_fast < 8 && (int64_t{1} << p.lg_fast) < fast_n) ++p.lg_fast;
-  const int64_t F = int64_t{1} << p.lg_fast, per = kThreads / F;
-  const int64_t gy = (slow_n + per - 1) / per;
-  const dim3 grid(static_cast<unsigned int>((fast_n + F - 1) / F),
-                  static_cast<unsigned int>(gy < 65535 ? gy : 65535));
-  if (t.words == 2) k_residues<2><<<grid, kThreads, 0, stream>>>(p);
-  else k_residues<3><<<grid, kThreads, 0, stream>>>(p);
+  const int64_t chunks = (e.k_hat + kQChunk - 1) / kQChunk;
+  const int64_t span_all = chunks * kQChunk;
+  if (o.rows_fast) {
+    p.lg_wpr = 0;  // a warp per row: the 8 rows of a CTA are adjacent in memory
+    p.k_span = span_all < 1024 ? span_all : 1024;
+  } else {
+    p.lg_wpr = 0;
+    while (p.lg_wpr < 3 && (int64_t{2} << p.lg_wpr) <= chunks) ++p.lg_wpr;
+    p.k_span = span_all;
+  }
+  const int64_t rows_per = kQWarps >> p.lg_wpr;
+  const int64_t gx = (p.rows_pad * p.batches + rows_per - 1) / rows_per;
+  const int64_t gy = fused ? 1 : (span_all + p.k_span - 1) / p.k_span;
+  if (gx > INT32_MAX || gy > 65535) return false;
+  const dim3 grid(static_cast<unsigned int>(gx), static_cast<unsigned int>(gy));
+  const int variant = (t.words == 2 ? 0 : 4) + (fused ? 2 : 0) + (e.trunc ? 1 : 0);
+  switch (variant) {
+    case 0: k_quantize<2, false, false><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 1: k_quantize<2, false, true><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 2: k_quantize<2, true, false><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 3: k_quantize<2, true, true><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 4: k_quantize<3, false, false><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 5: k_quantize<3, false, true><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 6: k_quantize<3, true, false><<<grid, kQThreads, 0, stream>>>(p); break;
+    default: k_quantize<3, true, true><<<grid, kQThreads, 0, stream>>>(p); break;
+  }
   return launched();
 }
 
@@ -829,7 +713,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     dest[x].sigma[0] = const_cast<int16_t*>(sX[x]);
     dest[x].flag[0] = const_cast<uint8_t*>(fX[x]);
     dest[x].res[0] = const_cast<int8_t*>(RX[x]);
-    if (run_scale && !from_pack[x] && !launch_scale(e, ov[x], dest[x], stream))
+    if (run_scale && !from_pack[x] && !fuses(ov[x]) && !launch_scale(e, ov[x], dest[x], stream))
       return IMD_STATUS_CUDA_ERROR;
   }
 
@@ -848,7 +732,9 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
         continue;
       }
       Rg[x] = RX[x];
-      if (!launch_residues(e, plan.res, ov[x], dest[x], g0, mods, stream))
+      // the launch of the first group of a call also computes the shifts of a fusing operand
+      const bool fused = run_scale && g0 == 0 && fuses(ov[x]);
+      if (!launch_quantize(e, plan.res, ov[x], dest[x], g0, mods, fused, stream))
         return IMD_STATUS_CUDA_ERROR;
     }
     mark(2, stream);
@@ -970,8 +856,8 @@ imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables
     d.flag[i] = base + layout.offset[1];
     d.res[i] = reinterpret_cast<int8_t*>(base + layout.offset[2]);
   }
-  if (!launch_scale(e, o, d, stream)) return IMD_STATUS_CUDA_ERROR;
-  if (!launch_residues(e, tables, o, d, 0, e.N, stream)) return IMD_STATUS_CUDA_ERROR;
+  if (!fuses(o) && !launch_scale(e, o, d, stream)) return IMD_STATUS_CUDA_ERROR;
+  if (!launch_quantize(e, tables, o, d, 0, e.N, fuses(o), stream)) return IMD_STATUS_CUDA_ERROR;
   mark(6, stream);
   return IMD_STATUS_SUCCESS;
 }

@@ -347,6 +347,7 @@ void pack_exec(const PackLowered& pl, ExecPlan* out) {
   if (pl.k >= 2) {
     e.rhs = shift_rhs(pl.N, pl.rounding == IMD_RN, static_cast<uint64_t>(pl.k));
     e.lhs_shift = pl.rounding == IMD_RN ? 2 : 0;
+    e.fast = shift_fast(e.rhs, static_cast<uint64_t>(pl.k));
   }
   // X as operand A: rows = R (class I), K, batch = L; strides in slot A only
   const int cls[3] = {kClsK, kClsL, kClsI};

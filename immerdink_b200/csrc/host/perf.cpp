@@ -142,10 +142,13 @@ void contract_phases(const Analysis& an, const ExecPlan& e, int32_t flags, int s
     const int32_t res_phase[2] = {IMD_PERF_PHASE_PACK_A, IMD_PERF_PHASE_PACK_B};
     for (int x = 0; x < 2; ++x) {
       if ((e.packed >> x) & 1) continue;
-      Phase& p = P->add(scale_phase[x], IMD_PERF_CLASS_KL, 1);
-      const double elems = d(e.b) * d(rows[x]) * d(e.k);
+      // only an operand that is contiguous along its rows has a scale launch of its own; the
+      // others get their shifts inside the first quantise launch (the phase stays, empty)
+      const bool own = e.rows_fast[x];
+      Phase& p = P->add(scale_phase[x], IMD_PERF_CLASS_KL, own ? 1 : 0);
+      const double elems = own ? d(e.b) * d(rows[x]) * d(e.k) : 0.0;
       p.bytes = 8.0 * elems;
-      p.x[0] = 1, p.x[1] = p.bytes, p.x[2] = elems;
+      p.x[0] = own ? 1 : 0, p.x[1] = p.bytes, p.x[2] = elems;
     }
     for (int x = 0; x < 2; ++x) {
       if ((e.packed >> x) & 1) continue;
@@ -170,9 +173,12 @@ void pack_phases(const PackLowered& pl, Phases* P) {
   Phase& prep = P->add(IMD_PERF_PHASE_PACK_PREP, IMD_PERF_CLASS_K0, 2);
   prep.bytes = 8.0 * (d(pl.r) + d(pl.k) + d(pl.b));
   prep.x[0] = 2, prep.x[1] = prep.bytes;
-  Phase& sc = P->add(IMD_PERF_PHASE_PACK_KL, IMD_PERF_CLASS_KL, 1);
-  sc.bytes = 8.0 * elems;
-  sc.x[0] = 1, sc.x[1] = sc.bytes, sc.x[2] = elems;
+  ExecPlan e;
+  pack_exec(pl, &e);
+  const bool own = e.rows_fast[0];  // as in contract_phases
+  Phase& sc = P->add(IMD_PERF_PHASE_PACK_KL, IMD_PERF_CLASS_KL, own ? 1 : 0);
+  sc.bytes = own ? 8.0 * elems : 0.0;
+  sc.x[0] = own ? 1 : 0, sc.x[1] = sc.bytes, sc.x[2] = own ? elems : 0.0;
   Phase& rs = P->add(IMD_PERF_PHASE_PACK_A, IMD_PERF_CLASS_PACK, 1);
   rs.bytes = 8.0 * elems + static_cast<double>(pl.layout.bytes[kPackRes]);
   rs.x[0] = 1, rs.x[1] = rs.bytes, rs.x[2] = elems * d(pl.N), rs.x[4] = elems;

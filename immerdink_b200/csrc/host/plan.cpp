@@ -137,6 +137,7 @@ imd_status_t make_plan(const Analysis& an, ExecPlan* out) {
   if (e.emulated()) {
     e.rhs = shift_rhs(e.N, rn, static_cast<uint64_t>(v.k));
     e.lhs_shift = rn ? 2 : 0;
+    e.fast = shift_fast(e.rhs, static_cast<uint64_t>(v.k));
     e.rows_fast[0] = rows_are_fast(v, kTenA);
     e.rows_fast[1] = rows_are_fast(v, kTenB);
     e.k_chunks = plan_k_chunks(e);
@@ -183,10 +184,16 @@ int64_t plan_kernel_launches(const ExecPlan& e) {
   const int64_t vec = e.vec_resident ? 0 : 1;
   if (!e.emulated()) return vec + 1;  // native FP64 kernel, or C <- beta C
   const int64_t groups = (e.N + e.g - 1) / e.g;
-  // vectors; one scale launch per operand; per group one residue launch per operand and the
-  // GEMM launches; one CRT launch.
-  const int64_t inline_ops = ((e.packed & 1) ? 0 : 1) + ((e.packed & 2) ? 0 : 1);
-  return vec + inline_ops + inline_ops * groups + plan_gemm_launches(e) + 1;
+  // vectors; per group one quantise launch per operand and the GEMM launches; one CRT launch.
+  // an in-line operand that is contiguous along its rows needs its own scale launch; the others
+  // get their shifts from the first quantise launch
+  int64_t inline_ops = 0, scale_launches = 0;
+  for (int x = 0; x < 2; ++x)
+    if (!(e.packed & (1 << x))) {
+      ++inline_ops;
+      if (e.rows_fast[x]) ++scale_launches;
+    }
+  return vec + scale_launches + inline_ops * groups + plan_gemm_launches(e) + 1;
 }
 
 uint64_t plan_host_bytes(const imd_tensor_t& A, const imd_tensor_t& B, const imd_tensor_t& C,

@@ -69,6 +69,7 @@ struct ExecPlan {
   Layout layout;
   Wide<8> rhs{};            // (2T - kappa)^2 2^60 or T^2 2^60
   int32_t lhs_shift = 0;    // S is multiplied by 4 (RN) or 1 (TRUNC): a left shift of 2 or 0
+  ShiftFast fast{};         // the same right-hand side for the FP64 shortcut of the shift rule
   bool rows_fast[2] = {false, false};  // operand is contiguous along its rows rather than along K
   bool c_batch_fast = false;           // C's batch mode is faster than its column mode
   int64_t vec_count = 0;
