@@ -98,6 +98,7 @@ imd_status_t plan_create(imd_handle_t handle, const imd_tensor_t* A, const imd_t
     if (e.emulated()) {
       imd::GemmPlanInfo info;
       if (const imd_status_t st = imd::gemm_setup(&info); st != IMD_STATUS_SUCCESS) return st;
+
       p->encode_tiled = info.encode_tiled;
       p->error_word = info.error_word;
     }
@@ -137,6 +138,8 @@ imd_status_t imd_create(imd_handle_t* handle) {
     cudaGetLastError();
     return IMD_STATUS_CUDA_ERROR;
   }
+  // per-device function attributes of the kernels are set here, never inside imd_contract / imd_pack
+  if (const imd_status_t st = imd::quantize_setup(); st != IMD_STATUS_SUCCESS) return st;
   auto* h = new (std::nothrow) imd_handle_st{device};
   if (h == nullptr) return IMD_STATUS_ALLOC_FAILED;
   *handle = h;

@@ -38,6 +38,7 @@ struct GemmPlanInfo {
   int sms = 0;
 };
 
+imd_status_t quantize_setup();                 // plan / pack creation: function attributes
 imd_status_t gemm_setup(GemmPlanInfo* info);   // plan time: function attributes, driver entry point
 imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int8_t* RA,
                          const int8_t* RB, uint8_t* W, cudaStream_t stream);

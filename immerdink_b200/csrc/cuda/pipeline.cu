@@ -473,6 +473,18 @@ bool& use_reference_gemm() {
   return v;
 }
 
+// Plan time: the fused quantise launches may use up to kQStageMax units of dynamic shared memory.
+imd_status_t quantize_setup() {
+  const int bytes = kQStageMax * kQStageBytes;
+  const bool ok =
+      cudaFuncSetAttribute(k_quantize<2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess &&
+      cudaFuncSetAttribute(k_quantize<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess &&
+      cudaFuncSetAttribute(k_quantize<3, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess &&
+      cudaFuncSetAttribute(k_quantize<3, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  if (!ok) cudaGetLastError();
+  return ok ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
 int& force_exact_shift() {
   static int v = 0;  // verification hook only
   return v;
@@ -628,6 +640,12 @@ bool launch_quantize(const ExecPlan& e, const ResidueTables& t, const OperandVie
     while (p.lg_wpr < 3 && (int64_t{2} << p.lg_wpr) <= chunks) ++p.lg_wpr;
     p.k_span = span_all;
   }
+  size_t smem = 0;
+  if (fused) {
+    const int64_t per_thread = (e.k_hat + (int64_t{256} << p.lg_wpr) - 1) / (int64_t{256} << p.lg_wpr);
+    p.stage_units = static_cast<int32_t>(per_thread < kQStageMax ? per_thread : kQStageMax);
+    smem = static_cast<size_t>(p.stage_units) * kQStageBytes;
+  }
   const int64_t rows_per = kQWarps >> p.lg_wpr;
   const int64_t gx = (p.rows_pad * p.batches + rows_per - 1) / rows_per;
   const int64_t gy = fused ? 1 : (span_all + p.k_span - 1) / p.k_span;
@@ -635,14 +653,14 @@ bool launch_quantize(const ExecPlan& e, const ResidueTables& t, const OperandVie
   const dim3 grid(static_cast<unsigned int>(gx), static_cast<unsigned int>(gy));
   const int variant = (t.words == 2 ? 0 : 4) + (fused ? 2 : 0) + (e.trunc ? 1 : 0);
   switch (variant) {
-    case 0: k_quantize<2, false, false><<<grid, kQThreads, 0, stream>>>(p); break;
-    case 1: k_quantize<2, false, true><<<grid, kQThreads, 0, stream>>>(p); break;
-    case 2: k_quantize<2, true, false><<<grid, kQThreads, 0, stream>>>(p); break;
-    case 3: k_quantize<2, true, true><<<grid, kQThreads, 0, stream>>>(p); break;
-    case 4: k_quantize<3, false, false><<<grid, kQThreads, 0, stream>>>(p); break;
-    case 5: k_quantize<3, false, true><<<grid, kQThreads, 0, stream>>>(p); break;
-    case 6: k_quantize<3, true, false><<<grid, kQThreads, 0, stream>>>(p); break;
-    default: k_quantize<3, true, true><<<grid, kQThreads, 0, stream>>>(p); break;
+    case 0: k_quantize<2, false, false><<<grid, kQThreads, smem, stream>>>(p); break;
+    case 1: k_quantize<2, false, true><<<grid, kQThreads, smem, stream>>>(p); break;
+    case 2: k_quantize<2, true, false><<<grid, kQThreads, smem, stream>>>(p); break;
+    case 3: k_quantize<2, true, true><<<grid, kQThreads, smem, stream>>>(p); break;
+    case 4: k_quantize<3, false, false><<<grid, kQThreads, smem, stream>>>(p); break;
+    case 5: k_quantize<3, false, true><<<grid, kQThreads, smem, stream>>>(p); break;
+    case 6: k_quantize<3, true, false><<<grid, kQThreads, smem, stream>>>(p); break;
+    default: k_quantize<3, true, true><<<grid, kQThreads, smem, stream>>>(p); break;
   }
   return launched();
 }

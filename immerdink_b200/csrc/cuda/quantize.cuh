@@ -30,6 +30,8 @@ constexpr int kQWarps = kQThreads / 32;
 constexpr int kQMaxSlots = (kMaxModuli + 1) / 2;  // a slot = two moduli (one mma column group)
 constexpr int kQChunk = 256;                      // K positions a warp handles per step
 constexpr int kMaxDests = 8;  // buffers one pack launch can write (the consumers of a slab)
+constexpr int kQStageBytes = kQThreads * 64;  // one unit (8 entries) of every thread
+constexpr int kQStageMax = 6;                 // units per thread: 96 KB, two CTAs per SM
 
 struct QuantParams {
   const double* X;
@@ -42,6 +44,7 @@ struct QuantParams {
   int64_t k_span;      // K positions per CTA (a multiple of 256; the whole row when fused)
   int32_t contig;      // how 8 adjacent K positions are found in memory (see load8)
   int32_t lg_wpr;      // log2 of the warps that share a row (8 >> lg_wpr rows per CTA)
+  int32_t stage_units; // fused: units of 8 entries per thread kept in shared memory for phase 2
   int32_t trunc;
   int32_t mod0, mods;  // first modulus and number of moduli of the group
   int32_t force_exact; // verification: never take the FP64 shortcut of the shift
@@ -133,6 +136,7 @@ __global__ void __launch_bounds__(kQThreads, 2) k_quantize(const __grid_constant
   __shared__ double s_acc[kQWarps];
   __shared__ uint64_t s_hi[kQWarps], s_lo[kQWarps];
   __shared__ int s_sigma[kQWarps], s_flag[kQWarps];
+  extern __shared__ uint4 s_stage[];  // fused launches: [unit][quarter][thread] of raw entries
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int W = 1 << p.lg_wpr;  // warps per row
@@ -176,23 +180,34 @@ __global__ void __launch_bounds__(kQThreads, 2) k_quantize(const __grid_constant
     uint32_t mx = 0;
     double acc = 0.0;
     if (live) {
-      double acc2 = 0.0;
+      // unit j of this thread = K positions 8 (32 (sub + W j) + lane) .. + 7: the same units it
+      // quantises in phase 2, so the first stage_units of them are parked in shared memory
+      // (thread-private slots) and phase 2 does not go back to L2 for them. Four units in flight.
       const int64_t stride = 8 * 32 * W;
-      for (int64_t Kt = 8 * static_cast<int64_t>(sub * 32 + lane); Kt < p.k; Kt += 2 * stride) {
-        uint64_t ra[8], rb[8];  // two units in flight
-        load8(p, base, Kt, ra);
-        load8(p, base, Kt + stride, rb);
+      const int64_t Kfirst = 8 * static_cast<int64_t>(sub * 32 + lane);
+      const int units = static_cast<int>((p.k_hat + stride - 1) / stride);  // zeros beyond k
+      int64_t Kt = Kfirst;
+      for (int j = 0; j < units; j += 4, Kt += 4 * stride) {
+        uint64_t ru[4][8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          mx = max(mx, static_cast<uint32_t>(ra[e] >> 32) & 0x7FFFFFFFu);
-          mx = max(mx, static_cast<uint32_t>(rb[e] >> 32) & 0x7FFFFFFFu);
-          const double xa = __longlong_as_double(static_cast<long long>(ra[e]));
-          const double xb = __longlong_as_double(static_cast<long long>(rb[e]));
-          acc = __fma_rn(xa, xa, acc);
-          acc2 = __fma_rn(xb, xb, acc2);
+        for (int u = 0; u < 4; ++u) load8(p, base, Kt + u * stride, ru[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            mx = max(mx, static_cast<uint32_t>(ru[u][e] >> 32) & 0x7FFFFFFFu);
+            const double x = __longlong_as_double(static_cast<long long>(ru[u][e]));
+            acc = __fma_rn(x, x, acc);
+          }
+          if (j + u < p.stage_units) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              s_stage[((j + u) * 4 + q) * kQThreads + tid] = make_uint4(
+                  static_cast<uint32_t>(ru[u][2 * q]), static_cast<uint32_t>(ru[u][2 * q] >> 32),
+                  static_cast<uint32_t>(ru[u][2 * q + 1]), static_cast<uint32_t>(ru[u][2 * q + 1] >> 32));
+          }
         }
       }
-      acc += acc2;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -325,8 +340,18 @@ __global__ void __launch_bounds__(kQThreads, 2) k_quantize(const __grid_constant
 #pragma unroll
   for (int e = 0; e < 8; ++e) raw[e] = 0;
   int64_t K0 = kbeg + static_cast<int64_t>(kQChunk) * sub;
-  if (live && K0 < kend) load8(p, base, K0 + 8 * lane, raw);
-  for (; K0 < kend; K0 += step) {
+  const int staged = FUSED ? p.stage_units : 0;
+  // chunk c of this warp is unit c of phase 1; unstaged chunks are loaded one step ahead
+  if (live && K0 < kend && staged == 0) load8(p, base, K0 + 8 * lane, raw);
+  for (int c = 0; K0 < kend; K0 += step, ++c) {
+    if (FUSED && c < staged && live) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 v = s_stage[(c * 4 + q) * kQThreads + tid];
+        raw[2 * q] = v.x | (static_cast<uint64_t>(v.y) << 32);
+        raw[2 * q + 1] = v.z | (static_cast<uint64_t>(v.w) << 32);
+      }
+    }
     // element e of this thread: K position K0 + 8 lane + e = tile e / 2, row g8 + 8 (e & 1),
     // element slot t4 of the mma operand
     uint32_t dl[8], dh[8], dt[8];
@@ -352,7 +377,7 @@ __global__ void __launch_bounds__(kQThreads, 2) k_quantize(const __grid_constant
       }
     }
     // the next chunk's loads travel while this one is reduced
-    if (live && K0 + step < kend) load8(p, base, K0 + step + 8 * lane, raw);
+    if (live && K0 + step < kend && c + 1 >= staged) load8(p, base, K0 + step + 8 * lane, raw);
     const bool in_k = K0 + kofs < p.k_hat;
     int64_t at = out0 + K0;
 #pragma unroll 2
