@@ -40,6 +40,7 @@ SIGNATURES = {
     "imd_contract_packed": [_P, C.c_double, C.POINTER(Operand), C.POINTER(Operand), C.c_double,
                             _P, _P, C.c_size_t, _P],
     "imd_wait_flags": [C.POINTER(C.c_void_p), C.c_int, C.c_uint, C.c_uint64, _P],
+    "imd_device_error": [C.POINTER(C.c_uint)],
     "imd_copy_if_flagged": [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_void_p),
                             C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32, _P],
 }
@@ -77,6 +78,14 @@ class Library:
                 break
             except OSError:
                 continue
+
+    def device_error(self):
+        """imd_device_error: the sticky device error word, read and cleared (synchronises)."""
+        v = C.c_uint(0)
+        st = self.lib.imd_device_error(C.byref(v))
+        if st:
+            raise RuntimeError(f"imd_device_error: status {st}")
+        return int(v.value)
 
     def current_device(self):
         if self.cudart is None:

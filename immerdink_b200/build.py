@@ -2,6 +2,7 @@
 
     libimmerdink_host.so   CUDA-free host queries        (g++)
     libimmerdink.so        C ABI + sm_100a kernels       (nvcc -gencode arch=compute_100a,code=sm_100a)
+    libimmerdink_hooks.so  the same objects + the imd_test_* / imd_prof_* entry points (tests, phase timing)
 
     python -m immerdink_b200.build [--force]
 
@@ -17,6 +18,8 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 HOST_LIB = os.path.join(HERE, "libimmerdink_host.so")
 CUDA_LIB = os.path.join(HERE, "libimmerdink.so")
+HOOKS_LIB = os.path.join(HERE, "libimmerdink_hooks.so")
+OBJ_DIR = os.path.join(HERE, "build")
 
 HOST_SOURCES = [os.path.join(CSRC, "host", f)
                 for f in ("lowering.cpp", "plan.cpp", "pack.cpp", "host_api.cpp", "accuracy.cpp", "perf.cpp",
@@ -64,18 +67,33 @@ def build_host(force=False):
 
 
 def build_cuda(force=False, verbose=False):
+    """Kernel and ABI objects are compiled once; hooks.cpp twice (with and without IMD_HOOKS); the
+    two libraries differ only in that object."""
     build_host(force)
     src_time = _newest([CSRC, INCLUDE])
-    if not force and os.path.exists(CUDA_LIB) and os.path.getmtime(CUDA_LIB) >= src_time:
+    if (not force and all(os.path.exists(p) and os.path.getmtime(p) >= src_time
+                          for p in (CUDA_LIB, HOOKS_LIB))):
         return CUDA_LIB
-    cmd = [_nvcc(), "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-ccbin", _cxx(),
-           "-I" + INCLUDE, "-I" + CSRC, *CUDA_SOURCES, "-o", CUDA_LIB,
-           "-L" + HERE, "-limmerdink_host", "-Xlinker", "-rpath=$ORIGIN"]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    common = [_nvcc(), "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+              "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-ccbin", _cxx(), "-I" + INCLUDE, "-I" + CSRC]
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    out = _run(cmd)
+        common[1:1] = ["-Xptxas", "-v"]
+    objs, out = [], ""
+    for src in CUDA_SOURCES:
+        obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < src_time:
+            out += _run(common + ["-c", src, "-o", obj])
+        objs.append(obj)
+    hooks_src = os.path.join(CSRC, "cuda", "hooks.cpp")
+    flavours = []
+    for lib, flag in ((CUDA_LIB, None), (HOOKS_LIB, "-DIMD_HOOKS")):
+        obj = os.path.join(OBJ_DIR, "hooks" + ("_on" if flag else "_off") + ".o")
+        out += _run(common + ([flag] if flag else []) + ["-c", hooks_src, "-o", obj])
+        flavours.append((lib, obj))
+    for lib, obj in flavours:
+        out += _run([_nvcc(), "-shared", "-ccbin", _cxx(), *objs, obj, "-o", lib,
+                     "-L" + HERE, "-limmerdink_host", "-Xlinker", "-rpath=$ORIGIN"])
     if verbose:
         print(out)
     return CUDA_LIB
@@ -90,3 +108,4 @@ if __name__ == "__main__":
     build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(HOST_LIB)
     print(CUDA_LIB)
+    print(HOOKS_LIB)

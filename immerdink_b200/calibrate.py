@@ -63,7 +63,8 @@ def main(argv=None):
     import immerdink_b200 as imd
     from immerdink_b200 import host
 
-    lib = imd.load_library()
+    from . import build as _build
+    lib = imd.load_library(_build.HOOKS_LIB)   # phase marks exist only in the instrumented library
     L = lib.lib
     dev = torch.device("cuda", torch.cuda.current_device())
     spec = "bik,bkj->bij"

@@ -399,52 +399,21 @@ imd_status_t imd_copy_if_flagged(const unsigned char* const* flags, const int64_
   return imd::enqueue_copy_if_flagged(flags, flag_bytes, num_ranges, dst, src, bytes, num_copies, stream);
 }
 
-/* ---- verification hooks (not part of the drop-in ABI) ---------------------------------------- */
-/* 1: run the slow exact int8 GEMM instead of the tensor-core kernel in later calls (cross-check). */
-IMD_API int imd_test_use_reference_gemm(int on) {
-  imd::use_reference_gemm() = on != 0;
-  return 0;
-}
-/* Benchmark-only: measured ceiling of the int8 tensor pipe (ops/s) for the GEMM's tile shapes. */
-IMD_API double imd_prof_mma_peak(int pair) {
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-    return 0.0;
-  return imd::mma_probe_tops(pair, sms);
-}
-IMD_API int imd_test_gemm_band_mb(int mb) {
-  if (mb > 0) imd::gemm_band_mb() = mb;
-  return imd::gemm_band_mb();
-}
-IMD_API int imd_test_gemm_l2_hints(int on) {
-  if (on >= 0) imd::gemm_l2_hints() = on;
-  return imd::gemm_l2_hints();
-}
-/* 1: later calls compute every shift from the exact 128-bit sum of squares (no FP64 shortcut). */
-IMD_API int imd_test_force_exact_shift(int on) {
-  imd::force_exact_shift() = on != 0;
-  return 0;
-}
-IMD_API int imd_test_gemm_variant(int v) {
-  imd::gemm_variant() = v;
-  return 0;
-}
-/* Reads (and clears) the sticky device error word: nonzero when a bounded wait in a kernel gave
- * up. Synchronises the device. */
-IMD_API unsigned int imd_test_device_error(void) {
+/* Extension: reads and clears the sticky device error word of the current device (bit 0 / 1: a
+ * bounded wait inside the GEMM kernels gave up, bit 2: imd_wait_flags ran out). Synchronises the
+ * device. */
+IMD_API imd_status_t imd_device_error(unsigned int* word) {
+  if (word == nullptr) return IMD_STATUS_INVALID_VALUE;
   unsigned int v = 0, zero = 0;
   unsigned int* p = imd::device_error_word();
-  if (p == nullptr || cudaDeviceSynchronize() != cudaSuccess) return 0xFFFFFFFFu;
-  cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost);
-  cudaMemcpy(p, &zero, sizeof zero, cudaMemcpyHostToDevice);
-  return v;
+  if (p == nullptr || cudaDeviceSynchronize() != cudaSuccess ||
+      cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess ||
+      cudaMemcpy(p, &zero, sizeof zero, cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
+  *word = v;
+  return IMD_STATUS_SUCCESS;
 }
-
-/* Benchmark-only phase timing: enable with an event capacity (0 disables); read sums the milliseconds
- * per phase tag since the last read (1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate,
- * 6 imd_pack). */
-IMD_API int imd_prof_enable(int capacity) { return imd::profile_enable(capacity); }
-IMD_API int imd_prof_read(float* ms_by_tag, int tags) { return imd::profile_read(ms_by_tag, tags); }
 
 }  // extern "C"

@@ -762,7 +762,7 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
                          const int8_t* RB, uint8_t* W, cudaStream_t stream) {
   if (info.encode_tiled == nullptr || info.error_word == nullptr) return IMD_STATUS_CUDA_ERROR;
   const EncodeTiled fn = reinterpret_cast<EncodeTiled>(info.encode_tiled);
-  const int variant = gemm_variant();
+  const int variant = hooks().gemm_variant;
   const bool pair = variant == 2 || (variant == 0 && s.m > kTileM);
   CUtensorMap map_a, map_b;
   if (!encode_planes(fn, &map_a, RA, s.k_hat, s.m, s.planes, kTileM) ||
@@ -777,12 +777,12 @@ imd_status_t gemm_launch(const GemmPlanInfo& info, const GemmShape& s, const int
     // rows of A that stay resident: about 32 MB of the 126 MB L2 (the B rows in flight, the
     // product tiles being written and the other die's copies share the rest)
     const int64_t tile_bytes = static_cast<int64_t>(pair ? 256 : kTileM) * (s.klen > 0 ? s.klen : 1);
-    int64_t rows = (static_cast<int64_t>(gemm_band_mb()) << 20) / tile_bytes;
+    int64_t rows = (static_cast<int64_t>(hooks().gemm_band_mb) << 20) / tile_bytes;
     rows = rows < 4 ? 4 : rows;
     p.band_rows = static_cast<int32_t>(rows < p.tiles_m ? rows : p.tiles_m);
     if (p.band_rows < 1) p.band_rows = 1;
   }
-  p.l2_hints = gemm_l2_hints();
+  p.l2_hints = hooks().gemm_l2_hints;
   p.W = W;
   p.error_word = info.error_word;
   const int64_t total = static_cast<int64_t>(s.planes) * p.tiles_m * p.tiles_n;
@@ -822,24 +822,6 @@ double mma_probe_tops(int pair, int sms) {
   const double issuers = pair ? grid / 2 : grid;
   const double ops = 2.0 * (pair ? 256.0 : 128.0) * 256.0 * 32.0 * iters * issuers;
   return ops / (ms * 1e-3);
-}
-
-int& gemm_band_mb() {
-  static int v = 32;  // tuning hook: MB of A rows kept L2-resident by the tile order
-  return v;
-}
-
-int& gemm_l2_hints() {
-  // Both operands "evict last": they are re-used across the band, the product planes written by
-  // the epilogue are not. Measured: about 2 % less launch time than without hints; "evict first"
-  // on the streamed operand multiplies the DRAM reads (its rows are still needed by the band).
-  static int v = 5;
-  return v;
-}
-
-int& gemm_variant() {
-  static int v = 0;  // verification hook: 0 = by shape, 1 = one CTA per tile, 2 = CTA pairs
-  return v;
 }
 
 }  // namespace imd

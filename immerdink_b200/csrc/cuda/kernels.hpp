@@ -78,24 +78,23 @@ constexpr int kMaxWaitFlags = 32;
 imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigned int expect,
                                 unsigned long long limit, cudaStream_t stream);
 
-// Verification switch: later calls run the slow exact GEMM instead of the tensor-core kernel.
-bool& use_reference_gemm();
-// Verification switch: 1 = the scale step never takes its FP64 shortcut (every row's shift comes
-// from the exact 128-bit sum), so that both ways can be compared on the same rows.
-int& force_exact_shift();
-// Verification switch for the tensor-core kernel: 0 = chosen by shape, 1 = one CTA per 128 x 256
-// tile, 2 = CTA pairs on 256 x 256 tiles.
-int& gemm_variant();
-// Tuning hook: MB of operand A's tile rows that the tile order keeps resident in L2 (default 32).
-int& gemm_band_mb();
-// Tuning hook: L2 eviction hints of the GEMM's operand loads (1: keep A's band, stream B).
-int& gemm_l2_hints();
+// Knobs of the verification and tuning hooks. The production library links a constant copy of the
+// defaults (nothing in it can change them: imd_contract consults no mutable process state); the
+// instrumented library used by the tests and by phase timing links a mutable copy with the
+// imd_test_* / imd_prof_* entry points (hooks.cpp, compiled twice).
+struct Hooks {
+  bool reference_gemm = false;  // run the slow exact GEMM instead of the tensor-core kernel
+  int gemm_variant = 0;         // 0 = by shape, 1 = one CTA per 128 x 256 tile, 2 = CTA pairs
+  int gemm_band_mb = 32;        // MB of operand A's tile rows the tile order keeps in L2
+  int gemm_l2_hints = 5;        // eviction hints of the GEMM's operand loads (evict last on both)
+  int force_exact_shift = 0;    // 1 = the scale step never takes its FP64 shortcut
+};
+const Hooks& hooks();
+// Phase boundary of a call (tags: 1 vectors + scale, 2 quantise, 3 GEMM, 4 CRT, 5 degenerate path,
+// 6 imd_pack): records an event in the instrumented library, nothing in the production one.
+void phase_mark(int tag, cudaStream_t stream);
 // Benchmark hook: int8 ops per second of back-to-back tcgen05.mma.kind::i8 with no loads.
 double mma_probe_tops(int pair, int sms);
-
-// Benchmark-only phase timing (tags: 1 vectors + scale, 2 residues, 3 GEMM, 4 CRT, 5 degenerate path, 6 imd_pack).
-int profile_enable(int capacity);
-int profile_read(float* ms_by_tag, int tags);
 
 // Sticky device-side error word (bounded waits that gave up); read by the verification hook.
 unsigned int* device_error_word();

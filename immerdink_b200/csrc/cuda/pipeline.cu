@@ -468,11 +468,6 @@ GemmShape gemm_shape(const ExecPlan& e, const uint32_t* crt_q, int mod0, int mod
   return s;
 }
 
-bool& use_reference_gemm() {
-  static bool v = false;  // verification hook only
-  return v;
-}
-
 // Plan time: the fused quantise launches may use up to kQStageMax units of dynamic shared memory.
 imd_status_t quantize_setup() {
   const int bytes = kQStageMax * kQStageBytes;
@@ -483,58 +478,6 @@ imd_status_t quantize_setup() {
       cudaFuncSetAttribute(k_quantize<3, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
   if (!ok) cudaGetLastError();
   return ok ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
-}
-
-int& force_exact_shift() {
-  static int v = 0;  // verification hook only
-  return v;
-}
-
-// Phase timing for the benchmark: when enabled, enqueue_contract records an event from a
-// preallocated pool on the caller's stream at every phase boundary. Off by default; one caller
-// at a time (the pool is process-global).
-namespace {
-struct PhaseProfile {
-  std::vector<cudaEvent_t> events;
-  std::vector<int> tags;
-  size_t used = 0;
-  bool on = false;
-} g_prof;
-void mark(int tag, cudaStream_t stream) {
-  if (!g_prof.on || g_prof.used >= g_prof.events.size()) return;
-  cudaEventRecord(g_prof.events[g_prof.used], stream);
-  g_prof.tags[g_prof.used++] = tag;
-}
-}  // namespace
-
-int profile_enable(int capacity) {
-  for (cudaEvent_t e : g_prof.events) cudaEventDestroy(e);
-  g_prof = PhaseProfile{};
-  if (capacity <= 0) return 0;
-  g_prof.events.resize(static_cast<size_t>(capacity));
-  g_prof.tags.assign(static_cast<size_t>(capacity), 0);
-  for (cudaEvent_t& e : g_prof.events)
-    if (cudaEventCreate(&e) != cudaSuccess) return 1;
-  g_prof.on = true;
-  return 0;
-}
-
-// ms_by_tag[t] += time of every segment that ENDS with an event tagged t; returns segments read.
-int profile_read(float* ms_by_tag, int tags) {
-  if (!g_prof.on || g_prof.used == 0) return 0;
-  cudaEventSynchronize(g_prof.events[g_prof.used - 1]);
-  int n = 0;
-  for (size_t i = 1; i < g_prof.used; ++i) {
-    const int t = g_prof.tags[i];
-    if (t <= 0 || t >= tags) continue;  // tag 0 opens a call: nothing ends there
-    float ms = 0;
-    if (cudaEventElapsedTime(&ms, g_prof.events[i - 1], g_prof.events[i]) == cudaSuccess) {
-      ms_by_tag[t] += ms;
-      ++n;
-    }
-  }
-  g_prof.used = 0;
-  return n;
 }
 
 namespace {
@@ -583,7 +526,7 @@ bool launch_scale(const ExecPlan& e, const OperandView& o, const PackDests& d, c
   p.rows_fast = o.rows_fast;
   p.lg_rt = scale_lg_rt(o.rows_fast, e.k, o.rows * e.b);
   p.lhs_shift = e.lhs_shift;
-  p.force_exact = force_exact_shift();
+  p.force_exact = hooks().force_exact_shift;
   p.rhs = e.rhs;
   p.fast = e.fast;
   p.out_rows = o.out_rows > 0 ? o.out_rows : o.rows;
@@ -617,7 +560,7 @@ bool launch_quantize(const ExecPlan& e, const ResidueTables& t, const OperandVie
   p.trunc = e.trunc;
   p.mod0 = mod0;
   p.mods = mods;
-  p.force_exact = force_exact_shift();
+  p.force_exact = hooks().force_exact_shift;
   p.lhs_shift = e.lhs_shift;
   p.rhs = e.rhs;
   p.fast = e.fast;
@@ -673,7 +616,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   const ExecPlan& e = plan.exec;
   char* base = static_cast<char*>(ws);
   auto region = [&](int r) { return base + e.layout.offset[r]; };
-  mark(0, stream);
+  phase_mark(0, stream);
   const int64_t* vec = e.vec_resident ? static_cast<const int64_t*>(plan.vec_dev)
                                       : reinterpret_cast<const int64_t*>(region(IMD_REGION_VEC));
   if (!e.vec_resident)
@@ -686,7 +629,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     const unsigned int grid = grid_for(e.b * e.m * e.n, 1 << 20);
     if (alpha == 0.0 || e.k == 0) k_beta<<<grid, kThreads, 0, stream>>>(p);
     else k_direct<<<grid, kThreads, 0, stream>>>(p);
-    mark(5, stream);
+    phase_mark(5, stream);
     return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
   }
 
@@ -735,7 +678,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
       return IMD_STATUS_CUDA_ERROR;
   }
 
-  mark(1, stream);
+  phase_mark(1, stream);
   GemmPlanInfo info;
   info.encode_tiled = plan.encode_tiled;
   info.error_word = static_cast<unsigned int*>(plan.error_word);
@@ -755,15 +698,15 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
       if (!launch_quantize(e, plan.res, ov[x], dest[x], g0, mods, fused, stream))
         return IMD_STATUS_CUDA_ERROR;
     }
-    mark(2, stream);
+    phase_mark(2, stream);
     for (int64_t c = 0; c < e.k_chunks; ++c) {
       const GemmShape s = gemm_shape(e, plan.crt.q, g0, mods, static_cast<int>(c));
-      const imd_status_t st = use_reference_gemm()
+      const imd_status_t st = hooks().reference_gemm
                                   ? gemm_reference_launch(s, Rg[0], Rg[1], W, stream)
                                   : gemm_launch(info, s, Rg[0], Rg[1], W, stream);
       if (st != IMD_STATUS_SUCCESS) return st;
     }
-    mark(3, stream);
+    phase_mark(3, stream);
   }
 
   if (!run_crt) return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
@@ -793,7 +736,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
 #undef IMD_CRT_CASE
     default: return IMD_STATUS_INVALID_VALUE;
   }
-  mark(4, stream);
+  phase_mark(4, stream);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
 
@@ -833,7 +776,7 @@ imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables
   if (n_dest < 1 || n_dest > kMaxDests) return IMD_STATUS_INVALID_VALUE;
   uint8_t* out = static_cast<uint8_t*>(dest[0]);
   int64_t* vec = static_cast<int64_t*>(ws);
-  mark(0, stream);
+  phase_mark(0, stream);
   VecParams vp;
   vp.modes = e.modes;
   vp.m = e.m, vp.n = 0, vp.k = e.k, vp.b = e.b;
@@ -876,7 +819,7 @@ imd_status_t enqueue_pack_scatter(const ExecPlan& e, const ResidueTables& tables
   }
   if (!fuses(o) && !launch_scale(e, o, d, stream)) return IMD_STATUS_CUDA_ERROR;
   if (!launch_quantize(e, tables, o, d, 0, e.N, fuses(o), stream)) return IMD_STATUS_CUDA_ERROR;
-  mark(6, stream);
+  phase_mark(6, stream);
   return IMD_STATUS_SUCCESS;
 }
 

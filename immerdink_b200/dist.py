@@ -535,7 +535,7 @@ class RankContraction:
         a second; the step that saw it computed on incomplete slabs and must be repeated."""
         from .device import load_library
         lib = getattr(self, "lib", None) or load_library(None)
-        return int(lib.lib.imd_test_device_error()) & 0xFFFFFFFF
+        return lib.device_error()
 
     def close(self):
         """Releases plans, packs and, with the residue exchange, the mappings and buffers (call it

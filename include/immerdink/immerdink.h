@@ -120,7 +120,7 @@ IMD_API imd_status_t imd_pack_scatter(imd_pack_t piece, const double* X, int64_t
  * small kernel that polls the num_flags (0..32) words flags[i] (device addresses, read at the
  * call) until each holds `expect`; work enqueued on `stream` afterwards sees the announced data.
  * The wait is bounded: after max_polls polls of a flag (0 = the default, about a second) the
- * kernel gives up, sets bit 2 (value 4) of the device error word (imd_test_device_error) and
+ * kernel gives up, sets bit 2 (value 4) of the device error word (imd_device_error) and
  * returns, so the stream always moves on. Checks: NULL -> INVALID_VALUE; num_flags outside 0..32
  * -> INVALID_VALUE; a flag address that is not 4-byte aligned -> MISALIGNED. */
 IMD_API imd_status_t imd_wait_flags(const unsigned int* const* flags, int num_flags,
@@ -160,6 +160,13 @@ IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
                                               const imd_operand_t* A, const imd_operand_t* B,
                                               double beta, double* C, void* ws, size_t ws_bytes,
                                               cudaStream_t stream, int32_t part);
+
+/* The sticky device error word (no counterpart in the reference: its kernels have no waits).
+ * Every wait inside this library's kernels is bounded; one that gives up sets a bit of a word in
+ * device memory and the kernel ends: bit 0 / bit 1 a barrier wait of the one-CTA / CTA-pair GEMM
+ * kernel, bit 2 imd_wait_flags. Reads the word of the current device into *word and clears it.
+ * Synchronises the device: a diagnostic, not part of a step. word == NULL -> INVALID_VALUE. */
+IMD_API imd_status_t imd_device_error(unsigned int* word);
 
 #ifdef __cplusplus
 }

@@ -33,14 +33,22 @@ class NotSupported(Exception):
     pass
 
 
+def reference_tree():
+    """Where the reference's source tree lies: $IMD_REFERENCE, else a directory `reference` beside
+    this repository; None when there is none (then only prebuilt files under _ref are used)."""
+    cand = os.environ.get("IMD_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src", "host")) else None
+
+
 def build(force=False):
     """Compile the C oracle (and the reference host library when its tree is present)."""
     src = os.path.join(HERE, "imd_oracle.c")
     stale = (not os.path.exists(LIB_PATH)
              or os.path.getmtime(LIB_PATH) < os.path.getmtime(src))
-    if force or stale or (os.path.isdir("/root/reference/src/host")
-                          and not os.path.exists(REF_HOST_PATH)):
-        subprocess.run(["make", "-C", HERE], check=True, capture_output=True)
+    ref = reference_tree()
+    if force or stale or (ref is not None and not os.path.exists(REF_HOST_PATH)):
+        subprocess.run(["make", "-C", HERE] + ([f"REF={ref}"] if ref else []), check=True,
+                       capture_output=True)
 
 
 _lib = None

@@ -8,6 +8,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
+# the tests drive the library through its verification hooks (imd_test_*, imd_prof_*), which only
+# the instrumented flavour exports; the production libimmerdink.so has none of them
+os.environ.setdefault("IMMERDINK_LIB", os.path.join(ROOT, "immerdink_b200", "libimmerdink_hooks.so"))
 
 
 def pytest_configure(config):

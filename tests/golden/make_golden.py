@@ -28,7 +28,9 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("IMD_REFERENCE", "")
+if not os.path.isdir(os.path.join(REF, "spec")):
+    raise SystemExit("usage: make_golden.py <path of the reference tree>  (or set IMD_REFERENCE)")
 sys.path.insert(0, os.path.join(REF, "spec"))
 import oracle as ro  # noqa: E402  (the reference's spec/oracle.py)
 

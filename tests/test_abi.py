@@ -26,9 +26,18 @@ def test_cuda_library_exports_header_and_refuses_without_gpu():
     build.build_cuda()
     lib = ctypes.CDLL(build.CUDA_LIB)
     names = declared("immerdink.h")
-    assert len(names) == 17 and sorted(_capi.SIGNATURES) == names  # the reference's 12 + five
+    assert len(names) == 18 and sorted(_capi.SIGNATURES) == names  # the reference's 12 + six
     for n in names + declared("immerdink_host.h"):
         getattr(lib, n)          # host symbols reachable through DT_NEEDED
+    # the production library exports no verification or profiling hook; the instrumented one does
+    import subprocess
+    def exported(path):
+        out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True).stdout
+        return {ln.split()[-1] for ln in out.splitlines() if " T " in ln and "imd_" in ln}
+    plain, hooked = exported(build.CUDA_LIB), exported(build.HOOKS_LIB)
+    assert plain == set(names)
+    extra = hooked - plain
+    assert extra and all(n.startswith(("imd_test_", "imd_prof_")) for n in extra)
     try:
         import torch
         if torch.cuda.is_available():

@@ -8,8 +8,13 @@ import sys
 
 import pytest
 
-REF_PY = "/root/reference/python"
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference's package: its tree ($IMD_REFERENCE or a directory `reference` beside the repository),
+# else the unmodified copy that oracle/Makefile stages under oracle/_ref/python
+_TREES = [os.environ.get("IMD_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"),
+          os.path.join(os.path.dirname(HERE), "oracle", "_ref")]
+REF_PY = next((os.path.join(t, "python") for t in _TREES
+               if os.path.isdir(os.path.join(t, "python", "immerdink"))), "")
 HOST_LIB = os.path.join(os.path.dirname(HERE), "immerdink_b200", "libimmerdink_host.so")
 
 SCRIPT = r"""
