@@ -41,6 +41,9 @@ SIGNATURES = {
                             _P, _P, C.c_size_t, _P],
     "imd_wait_flags": [C.POINTER(C.c_void_p), C.c_int, C.c_uint, C.c_uint64, _P],
     "imd_device_error": [C.POINTER(C.c_uint)],
+    "imd_device_error_peek": [C.c_void_p, _P],
+    "imd_push_ranges": [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32,
+                        C.POINTER(C.c_void_p), C.c_int32, C.c_uint, C.c_int32, _P],
     "imd_copy_if_flagged": [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_void_p),
                             C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32, _P],
 }

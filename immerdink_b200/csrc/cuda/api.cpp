@@ -399,6 +399,38 @@ imd_status_t imd_copy_if_flagged(const unsigned char* const* flags, const int64_
   return imd::enqueue_copy_if_flagged(flags, flag_bytes, num_ranges, dst, src, bytes, num_copies, stream);
 }
 
+/* Pushes by a small copy kernel (extension; see the header). */
+imd_status_t imd_push_ranges(void* const* dst, const void* const* src, const int64_t* bytes,
+                             int32_t num_ranges, unsigned int* const* flags, int32_t num_flags,
+                             unsigned int value, int32_t ctas, cudaStream_t stream) {
+  if (num_ranges < 0 || num_ranges > imd::kMaxPushRanges || num_flags < 0 ||
+      num_flags > imd::kMaxPushFlags || ctas < 0 || ctas > 1024)
+    return IMD_STATUS_INVALID_VALUE;
+  if (num_ranges == 0 && num_flags == 0) return IMD_STATUS_SUCCESS;
+  if ((num_ranges > 0 && (dst == nullptr || src == nullptr || bytes == nullptr)) ||
+      (num_flags > 0 && flags == nullptr))
+    return IMD_STATUS_INVALID_VALUE;
+  for (int r = 0; r < num_ranges; ++r) {
+    if (bytes[r] < 0 || (bytes[r] > 0 && (dst[r] == nullptr || src[r] == nullptr)))
+      return IMD_STATUS_INVALID_VALUE;
+    if (bytes[r] % 16 != 0 || reinterpret_cast<uintptr_t>(dst[r]) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(src[r]) % 16 != 0)
+      return IMD_STATUS_MISALIGNED;
+  }
+  for (int f = 0; f < num_flags; ++f) {
+    if (flags[f] == nullptr) return IMD_STATUS_INVALID_VALUE;
+    if (reinterpret_cast<uintptr_t>(flags[f]) % 4 != 0) return IMD_STATUS_MISALIGNED;
+  }
+  return imd::enqueue_push(dst, src, bytes, num_ranges, flags, num_flags, value, ctas > 0 ? ctas : 32,
+                           stream);
+}
+
+/* The device error word copied to pinned host memory in stream order (extension; see the header). */
+imd_status_t imd_device_error_peek(unsigned int* host_word, cudaStream_t stream) {
+  if (host_word == nullptr) return IMD_STATUS_INVALID_VALUE;
+  return imd::enqueue_error_peek(host_word, stream);
+}
+
 /* Extension: reads and clears the sticky device error word of the current device (bit 0 / 1: a
  * bounded wait inside the GEMM kernels gave up, bit 2: imd_wait_flags ran out). Synchronises the
  * device. */

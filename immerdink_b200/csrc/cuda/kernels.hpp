@@ -74,6 +74,16 @@ constexpr int kMaxCondCopies = 16;
 imd_status_t enqueue_copy_if_flagged(const unsigned char* const* flags, const int64_t* flag_bytes,
                                      int ranges, void* const* dst, const void* const* src,
                                      const int64_t* bytes, int copies, cudaStream_t stream);
+// One launch of `ctas` CTAs: copies the ranges src[r] -> dst[r] (16-byte aligned, bytes[r] multiples
+// of 16; destinations may be peers' memory), then stores `value` into the flag words (release,
+// system scope).
+constexpr int kMaxPushRanges = 96;
+constexpr int kMaxPushFlags = 8;
+imd_status_t enqueue_push(void* const* dst, const void* const* src, const int64_t* bytes, int ranges,
+                          unsigned int* const* flags, int num_flags, unsigned int value, int ctas,
+                          cudaStream_t stream);
+// Copies the device error word into *host_word (pinned host memory) on `stream`, without clearing it.
+imd_status_t enqueue_error_peek(unsigned int* host_word, cudaStream_t stream);
 constexpr int kMaxWaitFlags = 32;
 imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigned int expect,
                                 unsigned long long limit, cudaStream_t stream);

@@ -13,6 +13,7 @@
 // (DIRECT mode or k = 1). The sequence replaces the reference's enqueue_contract
 // (src/contract.cu:1334-1485) and its kernels K0, K1, K2/K3, KF, KL, K5, k_direct,
 // k5_beta_only; the numerics are in numerics.cuh.
+#include <atomic>
 #include <cstdint>
 #include <mutex>
 #include <vector>
@@ -835,17 +836,27 @@ struct WaitParams {
   int n;
   unsigned int expect;
   unsigned long long limit;
+  unsigned long long max_ns;
   unsigned int* error_word;
 };
 
 __global__ void k_wait_flags(WaitParams p) {
   const int i = threadIdx.x;
   if (i >= p.n) return;
+  // bounded twice: by the poll count and by about two seconds of the global timer, whichever
+  // comes first (a poll takes longer when the GPU is busy, the timer does not)
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (unsigned long long it = 0; it < p.limit; ++it) {
     unsigned int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flag[i]) : "memory");
     if (v == p.expect) return;
     __nanosleep(200);
+    if ((it & 1023) == 1023) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > p.max_ns) break;
+    }
   }
   atomicOr(p.error_word, 4u);
 }
@@ -857,10 +868,93 @@ imd_status_t enqueue_wait_flags(const unsigned int* const* flags, int n, unsigne
   WaitParams p;
   for (int i = 0; i < kMaxWaitFlags; ++i) p.flag[i] = i < n ? flags[i] : nullptr;
   p.n = n, p.expect = expect, p.limit = limit;
+  p.max_ns = 2000000000ull;
   p.error_word = device_error_word();
   if (p.error_word == nullptr) return IMD_STATUS_CUDA_ERROR;
   k_wait_flags<<<1, kMaxWaitFlags, 0, stream>>>(p);
   return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+// ---- pushes by a small copy kernel --------------------------------------------------------------
+// The residue exchange of the multi-GPU driver sends a rank's rows of the residue planes into
+// the other consumers' slab buffers while the GEMM of the previous residue group runs. One launch
+// of a few CTAs (they share the SMs with the persistent GEMM, which leaves threads and registers
+// free) copies every range with 16-byte loads and plain stores (destinations may be peers' memory
+// mapped into this process) and, after the last CTA has finished, writes `value` into the flag
+// words that tell the consumers. Order: every CTA fences its stores at system scope before it
+// counts itself done; the last one fences again and then stores the flags.
+namespace {
+
+constexpr int kPushTickets = 64;
+__device__ unsigned int g_push_done[kPushTickets];
+
+struct PushParams {
+  uint4* dst[kMaxPushRanges];
+  const uint4* src[kMaxPushRanges];
+  long long units[kMaxPushRanges];   // 16-byte units
+  int ranges;
+  unsigned int* flag[kMaxPushFlags];
+  int flags;
+  unsigned int value;
+  int ticket;
+};
+
+__global__ void __launch_bounds__(kThreads) k_push(const __grid_constant__ PushParams p) {
+  const long long step = static_cast<long long>(gridDim.x) * kThreads;
+  const long long first = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+  for (int r = 0; r < p.ranges; ++r) {
+    const uint4* __restrict__ src = p.src[r];
+    uint4* __restrict__ dst = p.dst[r];
+    const long long n = p.units[r];
+    long long i = first;
+    for (; i + 3 * step < n; i += 4 * step) {  // four loads in flight per thread
+      const uint4 a = src[i], b = src[i + step], c = src[i + 2 * step], d = src[i + 3 * step];
+      dst[i] = a, dst[i + step] = b, dst[i + 2 * step] = c, dst[i + 3 * step] = d;
+    }
+    for (; i < n; i += step) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(&g_push_done[p.ticket], 1u) + 1;
+    if (done == gridDim.x) {
+      g_push_done[p.ticket] = 0;  // the ticket is free again once this launch has ended
+      __threadfence_system();
+      for (int f = 0; f < p.flags; ++f)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[f]), "r"(p.value) : "memory");
+    }
+  }
+}
+
+std::atomic<unsigned int> g_push_ticket{0};
+
+}  // namespace
+
+imd_status_t enqueue_push(void* const* dst, const void* const* src, const int64_t* bytes, int ranges,
+                          unsigned int* const* flags, int num_flags, unsigned int value, int ctas,
+                          cudaStream_t stream) {
+  PushParams p = {};
+  p.ranges = ranges, p.flags = num_flags, p.value = value;
+  for (int r = 0; r < ranges; ++r) {
+    p.dst[r] = static_cast<uint4*>(dst[r]);
+    p.src[r] = static_cast<const uint4*>(src[r]);
+    p.units[r] = bytes[r] / 16;
+  }
+  for (int f = 0; f < num_flags; ++f) p.flag[f] = flags[f];
+  // launches that may overlap (different streams) count on different words
+  p.ticket = static_cast<int>(g_push_ticket.fetch_add(1) % kPushTickets);
+  k_push<<<ctas, kThreads, 0, stream>>>(p);
+  return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+}
+
+imd_status_t enqueue_error_peek(unsigned int* host_word, cudaStream_t stream) {
+  unsigned int* p = device_error_word();
+  if (p == nullptr) return IMD_STATUS_CUDA_ERROR;
+  if (cudaMemcpyAsync(host_word, p, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
+  return IMD_STATUS_SUCCESS;
 }
 
 // ---- copies that run only when a row is flagged ----------------------------------------------------
@@ -961,12 +1055,12 @@ IMD_API imd_status_t imd_contract_builtin_ws(imd_plan_t plan, double alpha, cons
                                              const double* B, double beta, double* C,
                                              cudaStream_t stream) {
   if (plan == nullptr) return IMD_STATUS_INVALID_VALUE;
-  if (plan->exec.layout.total > imd::kBuiltinWorkspaceBytes)
-    return IMD_STATUS_INSUFFICIENT_WORKSPACE;  // this contraction needs more than the fixed 32 MiB
   void* ws = nullptr;
   size_t bytes = 0;
   if (const imd_status_t st = imd::builtin_workspace(&ws, &bytes); st != IMD_STATUS_SUCCESS)
     return st;
+  // imd_contract's own checks in their documented order: a plan that needs more than the fixed
+  // 32 MiB fails its size test there (INSUFFICIENT_WORKSPACE), after the earlier checks
   return imd_contract(plan, alpha, A, B, beta, C, ws, bytes, stream);
 }
 

@@ -159,21 +159,22 @@ def _pointer(x, expected, stream, out=False, device=None):
 
 
 class Handle:
-    """imd_create on the current device."""
+    """A library handle (imd_create) bound to the device that is current when it is made. It is
+    released by close() or when the object is collected, whichever comes first."""
 
     def __init__(self, lib=None):
-        self.lib = load_library(lib)
-        self.device = self.lib.current_device()
-        h = ct.c_void_p()
-        st = self.lib.lib.imd_create(ct.byref(h))
-        if st:
-            raise _error(st, "imd_create")
-        self._h = h.value
-        self._fin = weakref.finalize(self, self.lib.lib.imd_destroy, h.value)
+        library = load_library(lib)
+        raw = ct.c_void_p()
+        status = library.lib.imd_create(ct.byref(raw))
+        if status != 0:
+            raise _error(status, "imd_create")
+        self.lib, self.device, self._h = library, library.current_device(), raw.value
+        self._fin = weakref.finalize(self, library.lib.imd_destroy, raw.value)
 
     def close(self):
-        self._h = None
-        self._fin()
+        if self._h is not None:
+            self._h = None
+            self._fin()
 
 
 _handles, _handles_lock = {}, threading.Lock()
@@ -232,19 +233,26 @@ class Pack:
         self._users = 0      # open plans made with this pack: they keep passing its handle
         self.closed = False
 
+    # A pack is destroyed (imd_pack_destroy) once it has been closed AND no open plan still
+    # passes its handle; `_users` counts those plans.
+    def _destroy_if_unused(self, unused):
+        if unused and self._h is not None:
+            self._h = None
+            self._fin()
+
     def _acquire(self):
+        """A plan starts using this pack."""
         with self._lock:
             if self.closed:
                 raise ValueError(f"{self!r} is closed")
             self._users += 1
 
     def _release(self):
+        """A plan made with this pack was closed or collected."""
         with self._lock:
             self._users -= 1
-            last = self.closed and self._users == 0
-        if last:
-            self._h = None
-            self._fin()
+            unused = self.closed and self._users == 0
+        self._destroy_if_unused(unused)
 
     @property
     def layout(self):
@@ -299,27 +307,26 @@ class Pack:
             raise _error(st, "imd_pack_scatter")
 
     def pack_ptr(self, X, packed, packed_bytes, ws, ws_bytes, stream=0):
-        """imd_pack with raw integers: only the C checks, no PackedBuffer record."""
+        """imd_pack on raw addresses: nothing is checked on the Python side and no PackedBuffer
+        record is left; the C entry point's own checks still apply."""
         if self.closed:
             raise ValueError(f"{self!r} is closed")
-        st = self._fn(self._h, X, packed, packed_bytes, ws, ws_bytes, stream)
-        if st:
-            raise _error(st, "imd_pack")
+        status = self._fn(self._h, X, packed, packed_bytes, ws, ws_bytes, stream)
+        if status != 0:
+            raise _error(status, "imd_pack")
 
     def close(self):
-        """Closed for new use at once; imd_pack_destroy runs when the last plan made with it is
-        closed or collected (those plans pass its handle at every call)."""
+        """No new use from now on; the handle itself lives until the last plan made with this pack
+        is closed or collected (such plans pass the handle at every call)."""
         with self._lock:
             self.closed = True
-            last = self._users == 0
-        if last:
-            self._h = None
-            self._fin()
+            unused = self._users == 0
+        self._destroy_if_unused(unused)
 
     def __enter__(self):
         return self
 
-    def __exit__(self, *exc):
+    def __exit__(self, exc_type, exc, tb):
         self.close()
 
     def __repr__(self):
@@ -328,71 +335,77 @@ class Pack:
 
 
 class PackedBuffer:
-    """A caller-owned packed buffer that remembers the pack last written into it by Pack.pack
-    (recorded on the host at enqueue). A plan refuses one whose record differs from its slot's
-    pack, and one with no record. A safety net for the plain stream-ordered pattern only: the
-    record follows host order, not GPU order. buf: a contiguous CUDA array, an (int pointer,
-    nbytes) tuple, or an int pointer with `nbytes`. (ref: python/immerdink/device.py:422-495)"""
+    """Caller-owned device memory for one packed operand, together with a host-side note of which
+    pack Pack.pack last enqueued into it. A packed plan checks that note against its slot before
+    every call and refuses (PackMismatchError) a buffer that was never packed or that holds a
+    different pack. The note is written in host order at enqueue time, so it protects the usual
+    single-stream use, not arbitrary multi-stream orderings.
+
+    `buf` is a contiguous CUDA array, a (pointer, nbytes) pair, or a bare integer pointer with
+    `nbytes`. Interface as in the reference's python/immerdink/device.py:422-495."""
 
     __slots__ = ("buf", "nbytes", "_last", "_lock")
 
     def __init__(self, buf, nbytes=None):
         if isinstance(buf, PackedBuffer):
-            raise TypeError("buf is already a PackedBuffer")
+            raise TypeError("wrap the underlying buffer, not another PackedBuffer")
         if buf is None:
-            raise ValueError("PackedBuffer needs a buffer")
+            raise ValueError("a PackedBuffer wraps existing device memory; got None")
+        size = None if nbytes is None else int(nbytes)
         if isinstance(buf, int):
-            if nbytes is None:
-                raise ValueError("a raw pointer needs nbytes")
-            buf = (buf, int(nbytes))
-        self.buf = buf
-        self.nbytes = None if nbytes is None else int(nbytes)
-        self._last = None
-        self._lock = threading.Lock()
+            if size is None:
+                raise ValueError("an integer pointer carries no size: pass nbytes as well")
+            buf = (buf, size)
+        self.buf, self.nbytes = buf, size
+        self._last, self._lock = None, threading.Lock()
 
     @property
     def last_pack(self):
+        """The PackRecord of the pack last written here by Pack.pack, or None."""
         return self._last
 
     def _resolve(self, what, writable, stream, device):
-        p, n = _arrays.buffer(self.buf, what, writable, stream, device)
-        if self.nbytes is not None:
-            if self.nbytes > n:
-                raise ValueError(f"{what}: nbytes {self.nbytes} > the buffer's {n} bytes")
-            n = self.nbytes
-        return p, n
+        """(pointer, usable bytes) of the wrapped memory; `nbytes`, when given, caps the size."""
+        ptr, have = _arrays.buffer(self.buf, what, writable, stream, device)
+        if self.nbytes is None:
+            return ptr, have
+        if have < self.nbytes:
+            raise ValueError(f"{what}: declared {self.nbytes} bytes but the buffer has only {have}")
+        return ptr, self.nbytes
 
     def _expect(self, rec, what):
+        """Raises PackMismatchError unless the noted pack equals `rec` (the plan slot's record)."""
         with self._lock:
-            got = self._last
-        if got == rec:
+            seen = self._last
+        if seen == rec:
             return
-        if got is None:
-            msg = "no pack recorded (written only by Pack.pack into this PackedBuffer)"
-        elif got.N != rec.N:
-            msg = f"buffer last packed at N={got.N}, plan expects N={rec.N}"
-        elif got.rounding != rec.rounding:
-            msg = f"buffer last packed with {got.rounding}, plan expects {rec.rounding}"
+        if seen is None:
+            why = "no pack recorded: only Pack.pack(X, this_buffer) leaves the record a plan looks for"
+        elif seen.N != rec.N:
+            why = f"holds a pack made with N={seen.N}, plan expects N={rec.N}"
+        elif seen.rounding != rec.rounding:
+            why = f"holds a pack made with rounding {seen.rounding}, plan expects {rec.rounding}"
         else:
-            msg = (f"buffer last packed with another key (digest {got.key_digest:#x}, "
-                   f"{got.pack_bytes} bytes), plan expects digest {rec.key_digest:#x}")
-        raise PackMismatchError(f"{what}: {msg}")
+            why = (f"holds the pack with key digest {seen.key_digest:#x} ({seen.pack_bytes} bytes), "
+                   f"plan expects key digest {rec.key_digest:#x}")
+        raise PackMismatchError(f"{what}: {why}")
 
     def __repr__(self):
-        r = self._last
-        return ("<immerdink_b200.PackedBuffer " +
-                ("never packed" if r is None else
-                 f"last packed at N={r.N} {r.rounding}, {r.pack_bytes} bytes") + ">")
+        seen = self._last
+        state = "empty" if seen is None else f"N={seen.N} {seen.rounding} pack of {seen.pack_bytes} bytes"
+        return f"<immerdink_b200.PackedBuffer {state}>"
 
 
 def _pack_specs(packs):
-    """(PackSpec or None, PackSpec or None) of packs given as Pack / PackSpec / None."""
+    """The two slots of a plan as host PackSpecs: each entry of `packs` may be a Pack, a PackSpec
+    or None; None (or a pair of Nones) means a plan without packed slots."""
     if packs is None:
         return None
-    if len(packs) != 2:
-        raise ValueError("packs = (pack of A or None, pack of B or None)")
-    out = tuple(p.spec if isinstance(p, Pack) else p for p in packs)
-    return None if out == (None, None) else out
+    slots = tuple(packs)
+    if len(slots) != 2:
+        raise ValueError("packs must have two entries: (for A, for B), each a Pack, PackSpec or None")
+    specs = tuple(getattr(entry, "spec", entry) if isinstance(entry, Pack) else entry for entry in slots)
+    return specs if any(sp is not None for sp in specs) else None
 
 
 def _finalize_plan(destroy, h, packs):
@@ -437,12 +450,11 @@ class Plan:
         self._cd = [host.CDesc(d) for d in descs]
         h = ct.c_void_p()
         L = self.lib.lib
-        held = []
+        held = []   # packs this plan has started to use: given back if creation fails
         try:
-            for pk in self.packs:
-                if pk is not None:
-                    pk._acquire()
-                    held.append(pk)
+            for pk in filter(None, self.packs):
+                pk._acquire()
+                held.append(pk)
             if self._packed:
                 hp = [None if p is None else p._h for p in self.packs]
                 st = L.imd_plan_create_packed(self.handle._h, self._cd[0].t, self._cd[1].t,
@@ -450,15 +462,15 @@ class Plan:
             else:
                 st = L.imd_plan_create(self.handle._h, self._cd[0].t, self._cd[1].t, self._cd[2].t,
                                        self._opt, ct.byref(h))
-            if st:
-                e = _error(st, "imd_plan_create" + ("_packed" if self._packed else ""))
-                if st == 8:
-                    e.reason = host.PACK_MISMATCH[self._lowering(check=False)["pack_mismatch"]]
-                    e.args = (e.args[0] + f" ({e.reason})",)
-                raise e
+            if st != 0:
+                failure = _error(st, "imd_plan_create_packed" if self._packed else "imd_plan_create")
+                if isinstance(failure, PackMismatchError):   # say which part of the key differs
+                    failure.reason = host.PACK_MISMATCH[self._lowering(check=False)["pack_mismatch"]]
+                    failure.args = (f"{failure.args[0]} ({failure.reason})",)
+                raise failure
         except BaseException:
-            for pk in held:
-                pk._release()
+            while held:
+                held.pop()._release()
             raise
         self._h = h.value
         self._fin = weakref.finalize(self, _finalize_plan, L.imd_plan_destroy, h.value, tuple(held))
@@ -485,11 +497,11 @@ class Plan:
         return self._lw
 
     def pack_spec(self, operand):
-        """imd_pack_desc_for of operand 0 (A) or 1 (B) for this plan's descriptors and options."""
-        o = self.options
-        return host.pack_desc_for(self.descs, operand=operand, N=o["N"], g=o["g"],
-                                  rounding=o["rounding"], mode=o["mode"], vec_mode=o["vec_mode"],
-                                  lib=self.lib.host)
+        """The pack spec (imd_pack_desc_for) under which operand 0 (A) or 1 (B) of THIS plan would
+        be packed: its descriptors with this plan's N, g, rounding, mode and vector mode."""
+        keep = ("N", "g", "rounding", "mode", "vec_mode")
+        return host.pack_desc_for(self.descs, operand=operand, lib=self.lib.host,
+                                  **{name: self.options[name] for name in keep})
 
     @property
     def host_bytes(self):
@@ -528,39 +540,44 @@ class Plan:
         return C
 
     def _operands(self, pa, pb, packed, s):
-        packed = (None, None) if packed is None else packed
-        if len(packed) != 2:
-            raise ValueError("packed = (buffer or None, buffer or None)")
-        ops = []
-        for x, (data, buf, pk) in enumerate(zip((pa, pb), packed, self.packs)):
-            if pk is None:
+        """The two imd_operand_t of a packed call: FP64 pointer plus, for a packed slot, the
+        packed memory (pointer, size) and the pack handle that names its layout."""
+        given = (None, None) if packed is None else tuple(packed)
+        if len(given) != 2:
+            raise ValueError("packed must have two entries: (buffer of A or None, buffer of B or None)")
+        records = []
+        for slot, fp64_ptr in enumerate((pa, pb)):
+            pack, buf, name = self.packs[slot], given[slot], f"packed[{slot}]"
+            if pack is None:
                 if buf is not None:
-                    raise ValueError(f"packed[{x}] given for an in-line operand")
-                ops.append(_capi.Operand(data, None, 0, None))
-                continue
-            if isinstance(buf, PackedBuffer):
-                buf._expect(pk.record, f"packed[{x}]")
-                p, n = buf._resolve(f"packed[{x}]", False, s, self.device)
-            elif isinstance(buf, tuple) or buf is None:
-                p, n = _arrays.buffer(buf, f"packed[{x}]")
+                    raise ValueError(f"{name} given for an in-line operand")
+                records.append(_capi.Operand(fp64_ptr, None, 0, None))
+            elif isinstance(buf, PackedBuffer):
+                buf._expect(pack.record, name)
+                ptr, size = buf._resolve(name, False, s, self.device)
+                records.append(_capi.Operand(fp64_ptr, ptr, size, pack._h))
             else:
-                p, n = _arrays.buffer(buf, f"packed[{x}]", False, s, self.device)
-            ops.append(_capi.Operand(data, p, n, pk._h))
-        return ct.byref(ops[0]), ct.byref(ops[1])
+                raw = buf is None or isinstance(buf, tuple)   # (pointer, size) pairs need no stream check
+                ptr, size = _arrays.buffer(buf, name) if raw else _arrays.buffer(buf, name, False, s, self.device)
+                records.append(_capi.Operand(fp64_ptr, ptr, size, pack._h))
+        return ct.byref(records[0]), ct.byref(records[1])
 
     def contract_ptr(self, alpha, A, B, beta, C, ws, ws_bytes, stream=0, packed=None, part=0):
-        """imd_contract with raw integers: only the C checks. packed = ((ptr, nbytes) or None,
-        ...) for a packed plan; part as in contract()."""
-        if self._packed and part:
-            st = self.lib.lib.imd_contract_packed_part(self._h, alpha, *self._operands(A, B, packed, stream),
-                                                       beta, C, ws, ws_bytes, stream, int(part))
-        elif self._packed:
-            st = self._fn(self._h, alpha, *self._operands(A, B, packed, stream), beta, C, ws,
-                          ws_bytes, stream)
+        """The C entry point on raw addresses (integers; `stream` a CUDA stream handle): no layout
+        or dtype check happens here, only those of the C side. For a packed plan, `packed` holds
+        one (pointer, nbytes) pair or None per operand and `part` selects a part of the call
+        (see contract())."""
+        if not self._packed:
+            status = self._fn(self._h, alpha, A, B, beta, C, ws, ws_bytes, stream)
         else:
-            st = self._fn(self._h, alpha, A, B, beta, C, ws, ws_bytes, stream)
-        if st:
-            raise self._fail(st, ws_bytes)
+            op_a, op_b = self._operands(A, B, packed, stream)
+            if part:
+                status = self.lib.lib.imd_contract_packed_part(self._h, alpha, op_a, op_b, beta, C, ws,
+                                                               ws_bytes, stream, int(part))
+            else:
+                status = self._fn(self._h, alpha, op_a, op_b, beta, C, ws, ws_bytes, stream)
+        if status != 0:
+            raise self._fail(status, ws_bytes)
 
     def _fail(self, st, nw):
         extra = ""
@@ -576,7 +593,7 @@ class Plan:
     def __enter__(self):
         return self
 
-    def __exit__(self, *exc):
+    def __exit__(self, exc_type, exc, tb):
         self.close()
 
     def __repr__(self):
@@ -627,11 +644,16 @@ class PlanCache:
                                            vec_mode=vec_mode, k4_tune=k4_tune, packs=packs, lib=lib))
 
     def clear(self):
+        """Forgets every plan. Plans that own device memory (RESIDENT vectors) are closed here;
+        the others are left to their finalizers, since callers may still hold them."""
         with self._lock:
-            plans, self._plans = list(self._plans.values()), {}
-        for p in {id(p): p for p in plans}.values():
-            if p.options["vec_mode"] == "RESIDENT":
-                p.close()
+            dropped = self._plans
+            self._plans = {}
+        seen = set()
+        for plan in dropped.values():
+            if id(plan) not in seen and plan.options["vec_mode"] == "RESIDENT":
+                plan.close()
+            seen.add(id(plan))
 
 
 default_plan_cache = PlanCache()

@@ -85,15 +85,18 @@ IMD_API imd_status_t imd_contract_packed(imd_plan_t plan, double alpha, const im
  * acceptable. The workspace is a fixed IMD_BUILTIN_WS_BYTES array inside the library image, so
  * every GPU that loads libimmerdink.so gives up that much memory until the process exits.
  *
- * Same checks, statuses and results as imd_contract, except that a plan whose imd_workspace_size
- * exceeds IMD_BUILTIN_WS_BYTES is refused with IMD_STATUS_INSUFFICIENT_WORKSPACE (nothing is
- * touched). The call allocates nothing, neither directly nor through a library.
+ * Same checks in the same order, statuses and results as imd_contract given that array and its
+ * size: a plan whose imd_workspace_size exceeds IMD_BUILTIN_WS_BYTES fails the size test at its
+ * usual place (IMD_STATUS_INSUFFICIENT_WORKSPACE, nothing touched). The call allocates nothing,
+ * neither directly nor through a library.
  *   - The first call on each device looks up the array's device address (the plan's device must be
  *     current, as for imd_contract); make that first call before any stream capture begins.
  *   - All calls on a device share the one array: two calls whose GPU work can overlap (different
  *     streams, or threads) race on it. Order them on one stream or with events.
  *   - The array keeps whatever the previous call left there. Nothing in it needs to start at zero:
- *     every byte a kernel reads is written earlier in the same call. */
+ *     every byte a kernel reads is written earlier in the same call.
+ *   - The looked-up address is cached per device for the life of the process; after a
+ *     cudaDeviceReset the library must be reloaded before this entry point is used again. */
 #define IMD_BUILTIN_WS_BYTES (32u << 20)
 IMD_API imd_status_t imd_contract_builtin_ws(imd_plan_t plan, double alpha, const double* A,
                                              const double* B, double beta, double* C,
@@ -161,12 +164,30 @@ IMD_API imd_status_t imd_contract_packed_part(imd_plan_t plan, double alpha,
                                               double beta, double* C, void* ws, size_t ws_bytes,
                                               cudaStream_t stream, int32_t part);
 
+/* Pushes by a small copy kernel (no counterpart in the reference; used by the multi-GPU driver).
+ * Enqueues ONE kernel of `ctas` CTAs (0 = 32; at most 1024) on `stream` that copies the
+ * num_ranges (0..96) ranges src[r] -> dst[r] of bytes[r] bytes with 16-byte loads and plain stores
+ * (destinations may be other GPUs' memory mapped into this process) and then, when every CTA has
+ * finished and fenced its stores at system scope, stores `value` into the num_flags (0..8) words
+ * flags[f] (release, system scope): what imd_wait_flags on the consumer's side waits for. The few
+ * CTAs run beside a persistent GEMM kernel on the same GPU. Checks: counts out of range, NULL
+ * arrays or NULL pointers of non-empty ranges -> INVALID_VALUE; a range that is not 16-byte
+ * granular or a flag that is not 4-byte aligned -> MISALIGNED. */
+IMD_API imd_status_t imd_push_ranges(void* const* dst, const void* const* src, const int64_t* bytes,
+                                     int32_t num_ranges, unsigned int* const* flags,
+                                     int32_t num_flags, unsigned int value, int32_t ctas,
+                                     cudaStream_t stream);
+
 /* The sticky device error word (no counterpart in the reference: its kernels have no waits).
  * Every wait inside this library's kernels is bounded; one that gives up sets a bit of a word in
  * device memory and the kernel ends: bit 0 / bit 1 a barrier wait of the one-CTA / CTA-pair GEMM
  * kernel, bit 2 imd_wait_flags. Reads the word of the current device into *word and clears it.
  * Synchronises the device: a diagnostic, not part of a step. word == NULL -> INVALID_VALUE. */
 IMD_API imd_status_t imd_device_error(unsigned int* word);
+/* The same word copied into *host_word (pinned host memory) in stream order, without clearing it
+ * and without synchronising: a driver that enqueues this at the end of every step sees, a step or
+ * two later, that a bounded wait of that step gave up. host_word == NULL -> INVALID_VALUE. */
+IMD_API imd_status_t imd_device_error_peek(unsigned int* host_word, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

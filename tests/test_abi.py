@@ -26,7 +26,7 @@ def test_cuda_library_exports_header_and_refuses_without_gpu():
     build.build_cuda()
     lib = ctypes.CDLL(build.CUDA_LIB)
     names = declared("immerdink.h")
-    assert len(names) == 18 and sorted(_capi.SIGNATURES) == names  # the reference's 12 + six
+    assert len(names) == 20 and sorted(_capi.SIGNATURES) == names  # the reference's 12 + eight
     for n in names + declared("immerdink_host.h"):
         getattr(lib, n)          # host symbols reachable through DT_NEEDED
     # the production library exports no verification or profiling hook; the instrumented one does

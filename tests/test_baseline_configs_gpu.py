@@ -83,7 +83,46 @@ def run(plan, A, B, C, alpha, beta, variant=0):
     del ws
 
 
-@pytest.mark.parametrize("n,N", [(16384, 14), (4096, 12), (4096, 16)])
+def test_config2_at_full_size_across_groups_variants_and_packs():
+    """'kjbc,kiac->abij', a=b=c=200, i=j=k=40 (8000^3 view), N = 14: a sampled block against the CPU
+    oracle, and every bit of C equal for g in {1, 7, 14}, both GEMM kernels, and a packed B."""
+    import torch
+    import immerdink_b200 as imd
+    spec = "kjbc,kiac->abij"
+    e = dict(a=200, b=200, c=200, i=40, j=40, k=40)
+    A = synth("uniform", 40 * 40 * 200 * 200, 11, "cuda").reshape(40, 40, 200, 200)
+    B = synth("uniform", 40 * 40 * 200 * 200, 12, "cuda").reshape(40, 40, 200, 200)
+    C = torch.full([e[c] for c in "abij"], float("nan"), dtype=torch.float64, device="cuda")
+    plan = imd.Plan(spec, A, B, C, N=14, g=7)
+    assert plan.workspace_bytes == 1792432896
+    run(plan, A, B, C, 1.0, 0.0)
+    sample_parity(plan.descs, (A, B), None, C, 1.0, 0.0, 14, rows=96, cols=96)
+    for g, variant in ((1, 2), (14, 1), (7, 1)):
+        p2 = imd.Plan(spec, A, B, C, N=14, g=g)
+        C2 = torch.full_like(C, float("nan"))
+        run(p2, A, B, C2, 1.0, 0.0, variant)
+        assert torch.equal(C2.view(torch.int64), C.view(torch.int64)), (g, variant)
+        p2.close()
+        del C2
+    pk = imd.Pack(plan.pack_spec(1))
+    buf = torch.empty(pk.pack_bytes + 256, dtype=torch.uint8, device="cuda")
+    off = (-buf.data_ptr()) % 256
+    pws = torch.empty(pk.workspace_bytes + 256, dtype=torch.uint8, device="cuda")
+    pwo = (-pws.data_ptr()) % 256
+    packed = imd.PackedBuffer(buf[off:off + pk.pack_bytes])
+    pk.pack(B, packed, workspace=pws[pwo:pwo + pk.workspace_bytes])
+    p3 = imd.Plan(spec, A, B, C, N=14, g=7, packs=(None, pk))
+    C3 = torch.full_like(C, float("nan"))
+    ws = torch.empty(p3.workspace_bytes + 256, dtype=torch.uint8, device="cuda")
+    wo = (-ws.data_ptr()) % 256
+    p3.contract(A, B, C3, workspace=ws[wo:wo + p3.workspace_bytes], packed=(None, packed))
+    torch.cuda.synchronize()
+    assert torch.equal(C3.view(torch.int64), C.view(torch.int64))
+    p3.close()
+    plan.close()
+
+
+@pytest.mark.parametrize("n,N", [(16384, 14), (16384, 12), (16384, 16), (4096, 12), (4096, 16)])
 def test_config3_square_gemm_wide_exponents(n, N):
     """'ik,kj->ij', entries sign x 2^e x u, alpha = 1.5, beta = 0.5, C prefilled uniform."""
     import torch
@@ -125,20 +164,30 @@ def test_config4_ladder_contraction_decaying_magnitudes():
     plan.close()
 
 
-def test_config5_strided_permuted_operand_reduced():
+@pytest.mark.parametrize("p,q,r,s,g", [(256, 64, 256, 128, 0), (1024, 64, 1024, 256, 1)],
+                         ids=["reduced", "full-138GB"])
+def test_config5_strided_permuted_operand(p, q, r, s, g):
     """'pqrs,sq->pr' with A stored in mode order (s,p,q,r), r fastest, a padded stride on the next
-    mode, bimodal values, N = 16. Reduced extents (the full configuration spans 138.5 GB)."""
+    mode, bimodal values, N = 16: at reduced extents and at the configuration's own (p = r = 1024,
+    q = 64, s = 256: a 138.5 GB operand, 17.2 GB of workspace at g = 1) where that much memory
+    can be had (skipped otherwise: nothing else is resident when it starts)."""
     import torch
     import immerdink_b200 as imd
     from immerdink_b200 import host
-    p, q, r, s = 256, 64, 256, 128
     rp = r + 8                                   # padded row: stride(q) = r + 8
+    torch.cuda.empty_cache()
+    need = s * p * q * rp * 8 + (20 << 30 if p > 256 else 1 << 30)
+    if torch.cuda.mem_get_info()[0] < need:
+        pytest.skip(f"needs {need >> 30} GiB of free device memory")
     strides = dict(r=1, q=rp, p=q * rp, s=p * q * rp)
-    buf = synth("bimodal", s * p * q * rp, 5, "cuda")
+    buf = torch.empty(s * p * q * rp, dtype=torch.float64, device="cuda")
+    for lo in range(0, buf.numel(), 1 << 27):    # bounded temporaries
+        n = min(1 << 27, buf.numel() - lo)
+        buf[lo:lo + n] = synth("bimodal", n, 5 + lo, "cuda")
     B = synth("bimodal", s * q, 6, "cuda").reshape(s, q)
     Cc = torch.full((p, r), float("nan"), dtype=torch.float64, device="cuda")
     A = imd.DeviceArray(buf.data_ptr(), (p, q, r, s), [strides[c] for c in "pqrs"])
-    plan = imd.Plan("pqrs,sq->pr", A, B, Cc, N=16)
+    plan = imd.Plan("pqrs,sq->pr", A, B, Cc, N=16, g=g)
     low = plan.lowering
     assert (low["m"], low["n"], low["k"], low["swapped"]) == (1, p * r, q * s, 1)
     run(plan, A, B, Cc, 1.0, 0.0)
