@@ -908,10 +908,13 @@ __global__ void __launch_bounds__(kThreads) k_push(const __grid_constant__ PushP
     const long long n = p.units[r];
     long long i = first;
     for (; i + 3 * step < n; i += 4 * step) {  // four loads in flight per thread
-      const uint4 a = src[i], b = src[i + step], c = src[i + 2 * step], d = src[i + 3 * step];
+      // streaming loads: the planes are read once here and must not push the GEMM's operand
+      // tiles out of L2
+      const uint4 a = __ldcs(src + i), b = __ldcs(src + i + step), c = __ldcs(src + i + 2 * step),
+                  d = __ldcs(src + i + 3 * step);
       dst[i] = a, dst[i + step] = b, dst[i + 2 * step] = c, dst[i + 3 * step] = d;
     }
-    for (; i < n; i += step) dst[i] = src[i];
+    for (; i < n; i += step) dst[i] = __ldcs(src + i);
   }
   __threadfence_system();
   __syncthreads();

@@ -77,6 +77,21 @@ def wait_flags(flags, expect, *, max_polls=0, stream=0, lib=None):
         raise _error(st, "imd_wait_flags")
 
 
+def push_ranges(copies, flags, value, *, ctas=0, stream=0, lib=None):
+    """imd_push_ranges: enqueue one small copy kernel that performs `copies` = [(dst, src, nbytes),
+    ...] (device addresses, 16-byte granular; destinations may be peers' memory) and then stores
+    `value` into the 32-bit words at the addresses `flags`."""
+    lib = load_library(lib)
+    nc, nf = len(copies), len(flags)
+    dst = (ct.c_void_p * max(nc, 1))(*[int(c[0]) for c in copies])
+    src = (ct.c_void_p * max(nc, 1))(*[int(c[1]) for c in copies])
+    nb = (ct.c_int64 * max(nc, 1))(*[int(c[2]) for c in copies])
+    fl = (ct.c_void_p * max(nf, 1))(*[int(f) for f in flags])
+    st = lib.lib.imd_push_ranges(dst, src, nb, nc, fl, nf, int(value), int(ctas), stream)
+    if st:
+        raise _error(st, "imd_push_ranges")
+
+
 def copy_if_flagged(flag_ranges, copies, *, stream=0, lib=None):
     """imd_copy_if_flagged: enqueue one kernel that performs `copies` = [(dst, src, nbytes), ...]
     (device addresses, 8-byte granular) only if a byte of `flag_ranges` = [(ptr, nbytes), ...] is

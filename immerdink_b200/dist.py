@@ -199,7 +199,8 @@ class RankContraction:
     the peers through CUDA IPC (cuda-python)."""
 
     def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
-                 exchange=None, push_streams=1, sync="flags", store_push="auto"):
+                 exchange=None, push_streams=1, sync="flags", store_push="auto", push="kernel",
+                 push_ctas=0):
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
@@ -247,9 +248,18 @@ class RankContraction:
             self.push_streams = [torch.cuda.Stream(dev) for _ in range(max(1, int(push_streams)))]
             # store_push = the operand (0 = A, 1 = B) whose planes the pack kernel itself stores into the
             # other consumers' buffers (NVLink stores) instead of the copy engines, or None
+            # push = "kernel": the planes travel by imd_push_ranges (a few CTAs beside the GEMM, NVLink
+            # stores, one launch per residue group that also sets the consumers' flag words);
+            # push = "copy": by the copy engines, one cudaMemcpyAsync per plane and flag
+            if push not in ("kernel", "copy"):
+                raise ValueError("push must be 'kernel' or 'copy'")
+            self.push, self.push_ctas = push, int(push_ctas)
+            if push == "kernel" and sync != "flags":
+                raise ValueError("push='kernel' announces by flag words: sync must be 'flags'")
             if store_push == "auto":   # one copy-engine stream carries about 350 GB/s in 8 MB copies: with
                 # three other consumers of one slab, the other slab's planes go by stores
-                store_push = None if max(part.pa, part.pb) < 4 else (0 if part.pa < part.pb else 1)
+                store_push = None if (push == "kernel" or max(part.pa, part.pb) < 4) else \
+                    (0 if part.pa < part.pb else 1)
             if store_push not in (None, 0, 1):
                 raise ValueError("store_push must be 'auto', None, 0 or 1")
             self.store_push = store_push
@@ -266,6 +276,10 @@ class RankContraction:
             # flags: the value a producer copies into a consumer's flag word after its planes
             self.values = torch.arange(1 << 16, dtype=torch.int32, device=dev)
             self.step = 0
+            # the device error word of the previous steps, mirrored into pinned host memory at the end
+            # of every step (imd_device_error_peek): a bounded flag wait that gave up surfaces as an
+            # exception from a later call instead of a silently wrong tile
+            self._err_host = torch.zeros(1, dtype=torch.int32).pin_memory()
             low = self.plan.lowering
             gg, NN = low["residue_group"], low["num_moduli"]
             self.groups_of_planes = [(l0, min(gg, NN - l0)) for l0 in range(0, NN, gg)]
@@ -400,8 +414,14 @@ class RankContraction:
             main.wait_event(b_in)
             return self.plan.contract(self.A, self.B, C, alpha=alpha, beta=beta, workspace=self.ws,
                                       stream=main, packed=(self.packed, None))
-        from .device import copy_if_flagged as _dev_copy_if, wait_flags as _dev_wait
+        from .device import copy_if_flagged as _dev_copy_if, push_ranges as _dev_push, wait_flags as _dev_wait
         rt, s = self._rt, main.cuda_stream
+        if int(self._err_host[0]) != 0:
+            word = self.device_error()        # synchronises and clears
+            self._err_host[0] = 0
+            raise RuntimeError(f"residue exchange: device error word {word:#x} after an earlier step (bit 2: a "
+                               "producer's planes did not arrive within the bounded wait); the tiles of that "
+                               "step and of those enqueued since are not valid: repeat them")
         shards = (shard_a, shard_b)
         kind = rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice
         # copies to different peers may go to different streams; all copies to one peer share one
@@ -410,10 +430,21 @@ class RankContraction:
         self.step = self.step % 65535 + 1     # 1..65535: never the value of an untouched flag word
         tick = self.step
 
-        def copy(j, dst, src, nbytes):
-            err, = rt.cudaMemcpyAsync(dst, src, nbytes, kind, pushes[j % len(pushes)].cuda_stream)
+        turn = [0]
+
+        def copy(j, dst, src, nbytes, on=None):
+            """One peer copy. Copies go to the push streams in turn (whatever their destination),
+            so that the fixed cost of one copy overlaps the transfer of another; `on` pins a stream."""
+            st = pushes[(turn[0] if on is None else on) % len(pushes)]
+            turn[0] += 1
+            err, = rt.cudaMemcpyAsync(dst, src, nbytes, kind, st.cuda_stream)
             if err != rt.cudaError_t.cudaSuccess:
                 raise RuntimeError(f"cudaMemcpyAsync to a peer: {err}")
+
+        def join():
+            """Stream 0 of the pushes waits for what the others hold so far."""
+            for st in pushes[1:]:
+                pushes[0].wait_event(st.record_event())
 
         def copy_rows(j, dst, src, off, rows, width, pitch):
             """`rows` runs of `width` bytes, `pitch` apart: contiguous copies (a few large runs;
@@ -428,10 +459,10 @@ class RankContraction:
         def word(x, position, slot):          # offset of a flag word inside a rank's flag buffer
             return 4 * ((x * _POSITIONS + position) * _SLOTS + slot)
 
-        def announce(x, j, slot, on=None):    # after the copies to consumer j of slab x: its flag word
-            if flags:
-                copy(j if on is None else on, self.flag_dests[x][j] + word(x, self.pos[x], slot),
-                     self.values.data_ptr() + 4 * tick, 4)
+        def announce(x, j, slot):             # after the copies to consumer j of slab x: its flag word
+            if flags:                         # on stream 0, which has joined the other push streams
+                copy(j, self.flag_dests[x][j] + word(x, self.pos[x], slot),
+                     self.values.data_ptr() + 4 * tick, 4, on=0)
 
         def await_(slot):                     # every other producer's copies of this slot have landed here
             ptrs = [self.flags + word(x, p, slot)
@@ -459,25 +490,47 @@ class RankContraction:
         # copy engines push the rows of the own pieces to the other consumers, group by group (the
         # first group of the operand packed first already while the other is being packed)
         arrived = []
+        by_kernel = self.push == "kernel" and flags
         for gi, (l0, mods) in enumerate(self.groups_of_planes):
             for x in order:
+                if not self.push_order[x]:    # nobody else consumes this slab
+                    continue
                 if gi == 0:
                     for st in pushes:
                         st.wait_event(packed_ev[x])
                 lay, R, b = self.slab[x].layout, self.slab_rows[x], self.slab[x].layout["b"]
                 rp, kh = self.piece[x].layout["r"], lay["k_hat"]
                 own = self.dests[x][0]
+                ranges, words = [], []        # push = "kernel": the operand's planes of the group in one launch
                 for j in self.push_order[x]:
                     dst = self.dests[x][1 + j]
                     if x == self.store_push:  # the pack kernel has stored the planes there already
-                        announce(x, j, gi)
+                        if by_kernel:
+                            words.append(self.flag_dests[x][j] + word(x, self.pos[x], gi))
+                        else:
+                            announce(x, j, gi)
                         continue
-                    if gi == 0:
+                    if gi == 0:               # shifts and flags: a few KB, by the copy engine
                         copy_rows(j, dst, own, lay["sig"][0] + 2 * self.row0[x], b, 2 * rp, 2 * R)
                         copy_rows(j, dst, own, lay["flag"][0] + self.row0[x], b, rp, R)
-                    copy_rows(j, dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b,
-                              rp * kh, R * kh)
-                    announce(x, j, gi)
+                    if by_kernel:
+                        off, width, pitch = lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, rp * kh, R * kh
+                        runs = [(off, mods * b * width)] if width == pitch else \
+                               [(off + r * pitch, width) for r in range(mods * b)]
+                        ranges += [(dst + o, own + o, n) for o, n in runs if n]
+                        words.append(self.flag_dests[x][j] + word(x, self.pos[x], gi))
+                    else:
+                        copy_rows(j, dst, own, lay["res"][0] + (l0 * b * R + self.row0[x]) * kh, mods * b,
+                                  rp * kh, R * kh)
+                if not by_kernel and x != self.store_push:
+                    join()                    # every plane of the group has left before a flag is set
+                    for j in self.push_order[x]:
+                        announce(x, j, gi)
+                if by_kernel and (ranges or words):
+                    for at in range(0, max(len(ranges), 1), 96):   # one launch unless there are more runs
+                        last = at + 96 >= len(ranges)
+                        _dev_push(ranges[at:at + 96], words if last else [], tick, ctas=self.push_ctas,
+                                  stream=pushes[0].cuda_stream, lib=self.lib)
             arrived.append(None if flags else [st.record_event() for st in pushes])
             self._mark(f"pushed group {gi}", pushes[0])
         # FP64 pieces: only the native path of non-finite rows reads them. Every rank stages its
@@ -485,10 +538,10 @@ class RankContraction:
         # consumers; a consumer fetches them only if a row flag of its slabs is set (below).
         piece_bytes = [shards[x].numel() * 8 for x in (0, 1)]
         for x in (0, 1):
-            copy(0, self.fp64_dests[x][0] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(), piece_bytes[x])
+            copy(0, self.fp64_dests[x][0] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(), piece_bytes[x], on=0)
         for x in (0, 1):
             for j in range(len(self.flag_dests[x])):
-                announce(x, j, _SLOTS - 1, on=0)
+                announce(x, j, _SLOTS - 1)
         fp64_in = [st.record_event() for st in pushes]
         self._mark("pushed fp64", pushes[0])
         packed = tuple(self.packed)
@@ -526,6 +579,10 @@ class RankContraction:
                      self.slab[x].layout["b"] * self.slab_rows[x]) for x in (0, 1)]
             _dev_copy_if(rows, fetch, stream=s, lib=self.lib)
         run(2)                                # native path of non-finite rows and columns
+        if flags:
+            st = self.lib.lib.imd_device_error_peek(self._err_host.data_ptr(), s)
+            if st:
+                raise RuntimeError(f"imd_device_error_peek: status {st}")
         self._mark("end", main)
         return C
 

@@ -87,3 +87,65 @@ def test_copy_if_flagged_copies_only_when_a_flag_byte_is_set():
         device.copy_if_flagged(ranges, [(dst.data_ptr() + 4, src.data_ptr(), 8)], stream=stream)
     with pytest.raises(imd.InvalidValueError):
         device.copy_if_flagged(ranges, copies * 9, stream=stream)
+
+
+def test_push_ranges_copies_then_sets_the_flags():
+    """imd_push_ranges on one GPU: every range arrives, the flag words hold the value afterwards,
+    and a wait on those words gets through."""
+    import torch
+    import immerdink_b200 as imd
+    from immerdink_b200 import device
+    lib = imd.load_library()
+    lib.device_error()
+    src = torch.arange(5 << 20, dtype=torch.float64, device="cuda")
+    dst = torch.zeros_like(src)
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    sizes = [16, 4096, (1 << 20) + 48, 7 << 20]     # bytes, 16-byte granular
+    copies, at = [], 0
+    for n in sizes:
+        copies.append((dst.data_ptr() + at, src.data_ptr() + at, n))
+        at += n + 64                                 # gaps stay untouched
+    side = torch.cuda.Stream()
+    words = [flags.data_ptr() + 4 * 2, flags.data_ptr() + 4 * 9]
+    for ctas in (0, 1, 7):
+        dst.zero_()
+        flags.zero_()
+        torch.cuda.synchronize()
+        device.push_ranges(copies, words, 41 + ctas, ctas=ctas, stream=side.cuda_stream)
+        side.synchronize()
+        device.wait_flags(words, 41 + ctas, stream=torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert lib.device_error() == 0
+        assert flags.tolist().count(41 + ctas) == 2 and int(flags.sum().item()) == 2 * (41 + ctas)
+        want = torch.zeros_like(src)
+        at = 0
+        for n in sizes:
+            want[at // 8:(at + n) // 8] = src[at // 8:(at + n) // 8]
+            at += n + 64
+        assert torch.equal(dst, want), ctas
+    device.push_ranges([], words, 5, stream=side.cuda_stream)     # flags only
+    torch.cuda.synchronize()
+    assert flags[2].item() == 5 and flags[9].item() == 5
+    with pytest.raises(imd.MisalignedError):
+        device.push_ranges([(dst.data_ptr() + 8, src.data_ptr(), 16)], [], 1, stream=side.cuda_stream)
+    with pytest.raises(imd.InvalidValueError):
+        device.push_ranges(copies * 25, [], 1, stream=side.cuda_stream)
+
+
+def test_device_error_peek_mirrors_the_word_into_pinned_memory():
+    import torch
+    import immerdink_b200 as imd
+    from immerdink_b200 import device
+    lib = imd.load_library()
+    lib.device_error()
+    host_word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.lib.imd_device_error_peek(host_word.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(host_word[0]) == 0
+    device.wait_flags([flag.data_ptr()], 9, max_polls=20, stream=stream)   # nothing sets it
+    assert lib.lib.imd_device_error_peek(host_word.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(host_word[0]) == 4                  # seen without clearing
+    assert lib.device_error() == 4 and lib.device_error() == 0
