@@ -18,7 +18,17 @@ piece), which the strided-tensor front end handles at no cost.
 import math
 from dataclasses import dataclass
 
-GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
+GRID = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}     # default grids (rows along la, columns along lb)
+
+
+def default_grid(world):
+    """(pa, pb) with pa * pb = world: the table above, else the most square factorisation with
+    pa <= pb (a prime world gives a one-axis split (1, world))."""
+    if world in GRID:
+        return GRID[world]
+    pa = max(d for d in range(1, int(math.isqrt(world)) + 1) if world % d == 0)
+    return pa, world // pa
+
 _POSITIONS, _SLOTS = 8, 32      # flag words per operand: producers sharing a slab x (residue groups + FP64)
 
 
@@ -32,6 +42,8 @@ class Partition:
     rank: int
     la: str
     lb: str
+    grid: tuple = None   # (pa, pb), pa * pb = world; None = default_grid(world). (1, world) splits C
+    #                      along lb only (every rank gathers all of B), (world, 1) along la only
 
     def __post_init__(self):
         ins, out = self.spec.replace(" ", "").split("->")
@@ -41,7 +53,9 @@ class Partition:
             raise ValueError(f"label {self.la!r} must be in B and C only")
         if not (self.lb in self.A and self.lb in self.C and self.lb not in self.B):
             raise ValueError(f"label {self.lb!r} must be in A and C only")
-        self.pa, self.pb = GRID[self.world]
+        self.pa, self.pb = self.grid if self.grid is not None else default_grid(self.world)
+        if self.pa < 1 or self.pb < 1 or self.pa * self.pb != self.world:
+            raise ValueError(f"grid {self.grid!r} does not have world = {self.world} ranks")
         self.ra, self.rb = self.rank // self.pb, self.rank % self.pb
         for lab, parts in ((self.la, self.world), (self.lb, self.world)):
             if self.extents[lab] % parts:
@@ -106,11 +120,11 @@ class Partition:
         return f"{specA},{specB}->{specC}", Layout(shapeA), Layout(shapeB), Layout(tuple(shapeC))
 
 
-def make_groups(world, dist):
+def make_groups(world, dist, grid=None):
     """Process groups, created by every rank in the same order: one per grid column (the ranks that
     share a slab of A) and one per grid row (a slab of B). Returns ({rb: group}, {ra: group});
-    a group of one rank is None."""
-    pa, pb = GRID[world]
+    a group of one rank is None. `grid` as in Partition."""
+    pa, pb = grid if grid is not None else default_grid(world)
     cols, rows = {}, {}
     for rb in range(pb):
         ranks = [ra * pb + rb for ra in range(pa)]

@@ -31,7 +31,7 @@ def _full_problem():
     return A, B
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, grid=None):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import imd_oracle as orc
@@ -39,7 +39,7 @@ def _worker(rank, world, port, out_dir):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    part = idist.Partition(SPEC, EXT, world, rank, "a", "b")
+    part = idist.Partition(SPEC, EXT, world, rank, "a", "b", grid)
     A, B = _full_problem()
     # this rank's pieces
     sa = part.shard_start(0)["b"]
@@ -48,7 +48,7 @@ def _worker(rank, world, port, out_dir):
     shard_b = torch.from_numpy(np.ascontiguousarray(B[:, :, sb:sb + part.piece_a, :]))
     out_a = torch.empty(part.gathered_shape(0), dtype=torch.float64)
     out_b = torch.empty(part.gathered_shape(1), dtype=torch.float64)
-    groups = idist.make_groups(world, dist)
+    groups = idist.make_groups(world, dist, grid)
     idist.gather(part, shard_a, shard_b, out_a, out_b, groups, dist)
     spec, la, lb, lc = part.plan_layouts()
     ins, outl = spec.split("->")
@@ -63,12 +63,13 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_partition_tiles_equal_the_undivided_result(world, tmp_path):
+@pytest.mark.parametrize("world,grid", [(2, None), (4, None), (8, None), (4, (1, 4)), (4, (4, 1)), (2, (2, 1))])
+def test_partition_tiles_equal_the_undivided_result(world, grid, tmp_path):
+    """Default grids and one-axis splits (C cut along one label only, the other operand gathered whole)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import imd_oracle as orc
-    port = 29500 + world + (os.getpid() % 1000)
-    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    port = 29500 + world + (os.getpid() % 1000) + (7 if grid else 0) + (grid[0] if grid else 0)
+    mp.spawn(_worker, args=(world, port, str(tmp_path), grid), nprocs=world, join=True)
     A, B = _full_problem()
     descs = []
     for lab in ("kjbc", "kiac", "abij"):
@@ -91,6 +92,11 @@ def test_partition_rejects_labels_of_the_wrong_class():
         Partition(SPEC, EXT, 2, 0, "k", "b")
     with pytest.raises(ValueError):
         Partition(SPEC, dict(EXT, a=7), 2, 0, "a", "b")
+    with pytest.raises(ValueError):
+        Partition(SPEC, EXT, 4, 0, "a", "b", (2, 4))          # 8 ranks' grid for a world of 4
+    from immerdink_b200.dist import default_grid
+    assert [default_grid(w) for w in (1, 2, 3, 4, 6, 7, 8, 12)] == [(1, 1), (1, 2), (1, 3), (2, 2), (2, 3),
+                                                                  (1, 7), (2, 4), (3, 4)]
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
