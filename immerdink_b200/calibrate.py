@@ -79,7 +79,7 @@ def main(argv=None):
             Cd = torch.zeros((b, m, n), dtype=torch.float64, device=dev)
             last = (b, m, n, k)
         ext = dict(b=b, i=m, j=n, k=k)
-        plan = imd.Plan(spec, A, B, Cd, N=N, g=g)
+        plan = imd.Plan(spec, A, B, Cd, N=N, g=g, lib=lib)
         ws = torch.empty(max(plan.workspace_bytes, 1), dtype=torch.uint8, device=dev)
 
         def call():
@@ -90,17 +90,18 @@ def main(argv=None):
         assert pred["status"] == "SUCCESS" and pred["dispatch"] == "EMULATE", pred["status"]
         ph = {p["phase"]: p for p in pred["phases"]}
         sc = [ph["K0 vec"], ph["KL A"], ph["KL B"]]
-        rows["scale"].append((t[1], [3.0, sc[0]["x"][1], sc[1]["x"][2] + sc[2]["x"][2]]))
+        rows["scale"].append((t[1], [float(sum(q["launches"] for q in sc)), sc[0]["x"][1],
+                                     sc[1]["x"][2] + sc[2]["x"][2]]))
         rs = [ph["K2 pack A"], ph["K3 pack B"]]
         rows["res"].append((t[2], [rs[0]["x"][0] + rs[1]["x"][0], rs[0]["x"][2] + rs[1]["x"][2],
-                                   rs[0]["x"][4] + rs[1]["x"][4]]))
+                                   rs[0]["x"][4] + rs[1]["x"][4], rs[0]["x"][3] + rs[1]["x"][3]]))
         rows["gemm"].append((t[3], [ph["K4 gemm"]["x"][0], ph["K4 gemm"]["x"][1]], ph["K4 gemm"]["x"][4],
                              ph["K4 gemm"]["launches"]))
         rows["crt"].append((t[4], [1.0, ph["K5 crt"]["x"][2]]))
         plan.close()
         if (N, g) == (14, 7):
             # imd_pack of A; DIRECT mode; the beta-only call
-            pk = imd.Pack(imd.pack_spec(spec, A, B, Cd, operand=0, N=N))
+            pk = imd.Pack(imd.pack_spec(spec, A, B, Cd, operand=0, N=N, lib=lib), lib=lib)
             buf = torch.empty(max(pk.pack_bytes, 1), dtype=torch.uint8, device=dev)
             pw = torch.empty(max(pk.workspace_bytes, 1), dtype=torch.uint8, device=dev)
             tp = measure(lambda: (flush.fill_(1), pk.pack(A, buf, workspace=pw)), L, (6,), args.steps)
@@ -108,7 +109,7 @@ def main(argv=None):
             rows["pack"].append((tp[6], pp))
             pk.close()
             if m * n * k * b <= 2e10:
-                pd = imd.Plan(spec, A, B, Cd, N=N, mode="DIRECT")
+                pd = imd.Plan(spec, A, B, Cd, N=N, mode="DIRECT", lib=lib)
                 wd = torch.empty(max(pd.workspace_bytes, 1), dtype=torch.uint8, device=dev)
                 td = measure(lambda: (flush.fill_(1), pd.contract(A, B, Cd, workspace=wd)), L, (5,), args.steps)
                 xd = {p["phase"]: p for p in host.predict(spec, ext, N=N, mode="DIRECT")["phases"]}
@@ -126,7 +127,7 @@ def main(argv=None):
     # it; the class parameters are then fitted to what is left of each phase.
     tiny = [i for i, r in enumerate(rows["crt"]) if r[1][1] <= 14 * 1e5]
     per_launch = [(rows["scale"][i][0] + rows["res"][i][0] + rows["gemm"][i][0] + rows["crt"][i][0]) /
-                  (3 + rows["res"][i][1][0] + rows["gemm"][i][3] + 1) for i in tiny]
+                  (rows["scale"][i][1][0] + rows["res"][i][1][0] + rows["gemm"][i][3] + 1) for i in tiny]
     launch = float(np.median(per_launch)) if per_launch else 5000.0
 
     def fit(y, X, launches):
@@ -149,16 +150,16 @@ def main(argv=None):
     P[CALL + 1] = launch
     n = len(rows["crt"])
     P[KL + 2] = fit([rows["scale"][i][0] for i in range(n)],
-                    [[rows["scale"][i][1][2]] for i in range(n)], [3] * n)[0]
+                    [[rows["scale"][i][1][2]] for i in range(n)], [rows["scale"][i][1][0] for i in range(n)])[0]
     # residues: the in-line launches and, with the scale part of the model taken out, imd_pack
     y = [rows["res"][i][0] for i in range(n)]
-    X = [[rows["res"][i][1][1], rows["res"][i][1][2]] for i in range(n)]
+    X = [[rows["res"][i][1][1], rows["res"][i][1][2], rows["res"][i][1][3]] for i in range(n)]
     nl = [rows["res"][i][1][0] for i in range(n)]
     for tp, pp in rows["pack"]:
         y.append(tp - pp["pack KL"]["x"][2] * P[KL + 2])
-        X.append([pp["K2 pack A"]["x"][2], pp["K2 pack A"]["x"][4]])
-        nl.append(4)
-    P[PACK + 2], P[PACK + 4] = fit(y, X, nl)
+        X.append([pp["K2 pack A"]["x"][2], pp["K2 pack A"]["x"][4], pp["K2 pack A"]["x"][3]])
+        nl.append(2 + pp["pack KL"]["launches"] + 1)
+    P[PACK + 2], P[PACK + 4], P[PACK + 3] = fit(y, X, nl)
     cg = fit([rows["gemm"][i][0] for i in range(n)], [rows["gemm"][i][1] for i in range(n)],
              [rows["gemm"][i][3] for i in range(n)])
     P[K4 + 0], P[K4 + 1], P[K4 + 4] = cg[0], cg[1], dram_ns
@@ -171,8 +172,9 @@ def main(argv=None):
                           [2] * len(rows["beta"]))[0]
 
     def model(i):
-        sc = 3 * launch + rows["scale"][i][1][2] * P[KL + 2]
-        rs = rows["res"][i][1][0] * launch + rows["res"][i][1][1] * P[PACK + 2] + rows["res"][i][1][2] * P[PACK + 4]
+        sc = rows["scale"][i][1][0] * launch + rows["scale"][i][1][2] * P[KL + 2]
+        rs = (rows["res"][i][1][0] * launch + rows["res"][i][1][1] * P[PACK + 2] + rows["res"][i][1][2] * P[PACK + 4] +
+              rows["res"][i][1][3] * P[PACK + 3])
         gm = rows["gemm"][i][3] * launch + max(np.dot(rows["gemm"][i][1], [P[K4], P[K4 + 1]]),
                                                rows["gemm"][i][2] * dram_ns)
         cr = launch + rows["crt"][i][1][1] * P[K5 + 2]
@@ -212,8 +214,9 @@ def main(argv=None):
     text = host.calib_format(cal)
     host.calib_parse(text)      # must parse back
     for tp, pp in rows["pack"]:
-        pr = (4 * launch + pp["pack KL"]["x"][2] * P[KL + 2] + pp["K2 pack A"]["x"][2] * P[PACK + 2] +
-              pp["K2 pack A"]["x"][4] * P[PACK + 4])
+        pr = ((3 + pp["pack KL"]["launches"]) * launch + pp["pack KL"]["x"][2] * P[KL + 2] +
+              pp["K2 pack A"]["x"][2] * P[PACK + 2] + pp["K2 pack A"]["x"][4] * P[PACK + 4] +
+              pp["K2 pack A"]["x"][3] * P[PACK + 3])
         print(f"pack: measured {tp / 1e3:.1f} us, model {pr / 1e3:.1f} us", file=sys.stderr)
     for (t, q) in tot:
         print(f"call: predicted {t * 1e3:.3f} ms, measured/predicted {q:.3f}", file=sys.stderr)

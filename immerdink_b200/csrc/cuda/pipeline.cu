@@ -577,11 +577,11 @@ bool launch_quantize(const ExecPlan& e, const ResidueTables& t, const OperandVie
   const int64_t chunks = (e.k_hat + kQChunk - 1) / kQChunk;
   const int64_t span_all = chunks * kQChunk;
   if (o.rows_fast) {
-    p.lg_wpr = 0;  // a warp per row: the 8 rows of a CTA are adjacent in memory
+    p.lg_wpr = 0;  // a warp per row: the rows of a CTA are adjacent in memory
     p.k_span = span_all < 1024 ? span_all : 1024;
   } else {
     p.lg_wpr = 0;
-    while (p.lg_wpr < 3 && (int64_t{2} << p.lg_wpr) <= chunks) ++p.lg_wpr;
+    while (p.lg_wpr < kQLgWarps && (int64_t{2} << p.lg_wpr) <= chunks) ++p.lg_wpr;
     p.k_span = span_all;
   }
   size_t smem = 0;

@@ -25,13 +25,15 @@
 namespace imd {
 namespace {
 
-constexpr int kQThreads = 256;
-constexpr int kQWarps = kQThreads / 32;
+constexpr int kQLgWarps = 2;                      // four warps per CTA: four CTAs of 128 registers per SM,
+constexpr int kQWarps = 1 << kQLgWarps;           // in different phases (one waits for DRAM, three compute)
+constexpr int kQThreads = 32 * kQWarps;
+constexpr int kQCtasPerSm = 4;
 constexpr int kQMaxSlots = (kMaxModuli + 1) / 2;  // a slot = two moduli (one mma column group)
 constexpr int kQChunk = 256;                      // K positions a warp handles per step
 constexpr int kMaxDests = 8;  // buffers one pack launch can write (the consumers of a slab)
 constexpr int kQStageBytes = kQThreads * 64;  // one unit (8 entries) of every thread
-constexpr int kQStageMax = 6;                 // units per thread: 96 KB, two CTAs per SM
+constexpr int kQStageMax = 6;                 // units per thread: 48 KB per CTA, four CTAs per SM
 
 struct QuantParams {
   const double* X;
@@ -43,7 +45,7 @@ struct QuantParams {
   int64_t plane_rows, row0, sigma_rows;
   int64_t k_span;      // K positions per CTA (a multiple of 256; the whole row when fused)
   int32_t contig;      // how 8 adjacent K positions are found in memory (see load8)
-  int32_t lg_wpr;      // log2 of the warps that share a row (8 >> lg_wpr rows per CTA)
+  int32_t lg_wpr;      // log2 of the warps that share a row (kQWarps >> lg_wpr rows per CTA)
   int32_t stage_units; // fused: units of 8 entries per thread kept in shared memory for phase 2
   int32_t trunc;
   int32_t mod0, mods;  // first modulus and number of moduli of the group
@@ -128,7 +130,7 @@ __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, ui
 }
 
 template <int WORDS, bool FUSED, bool TRUNC>
-__global__ void __launch_bounds__(kQThreads, 2) k_quantize(const __grid_constant__ QuantParams p) {
+__global__ void __launch_bounds__(kQThreads, kQCtasPerSm) k_quantize(const __grid_constant__ QuantParams p) {
   __shared__ uint32_t s_b[WORDS][kQMaxSlots][32];  // B fragments (digit weights) by slot and lane
   __shared__ float s_inv[kQMaxSlots][2];
   __shared__ int s_negp[kQMaxSlots][2];

@@ -156,6 +156,7 @@ void contract_phases(const Analysis& an, const ExecPlan& e, int32_t flags, int s
       const double elems = d(e.b) * d(rows[x]) * d(e.k);
       p.bytes = 8.0 * elems * d(groups) + d(e.N) * d(e.b) * d(rows_pad[x]) * d(e.k_hat);
       p.x[0] = d(groups), p.x[1] = p.bytes, p.x[2] = elems * d(e.N), p.x[4] = elems * d(groups);
+      p.x[3] = e.rows_fast[x] ? 0.0 : elems;  // the scan of the fused first launch (shift of the rows)
     }
     gemm_features(e, sms, &P->add(IMD_PERF_PHASE_K4, IMD_PERF_CLASS_K4_128x256, 0));
     P->launches += P->list.back().launches;
@@ -182,6 +183,7 @@ void pack_phases(const PackLowered& pl, Phases* P) {
   Phase& rs = P->add(IMD_PERF_PHASE_PACK_A, IMD_PERF_CLASS_PACK, 1);
   rs.bytes = 8.0 * elems + static_cast<double>(pl.layout.bytes[kPackRes]);
   rs.x[0] = 1, rs.x[1] = rs.bytes, rs.x[2] = elems * d(pl.N), rs.x[4] = elems;
+  rs.x[3] = own ? 0.0 : elems;
   Phase& call = P->add(IMD_PERF_PHASE_CALL, IMD_PERF_CLASS_CALL, 0);
   call.x[0] = 1, call.x[1] = d(P->launches);
 }
