@@ -213,7 +213,7 @@ class RankContraction:
     the peers through CUDA IPC (cuda-python)."""
 
     def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
-                 exchange=None, push_streams=1, sync="flags", store_push="auto", push="kernel",
+                 exchange=None, push_streams=1, sync="flags", store_push="auto", push="copy",
                  push_ctas=0):
         import torch
         from . import device as _dev
@@ -262,9 +262,12 @@ class RankContraction:
             self.push_streams = [torch.cuda.Stream(dev) for _ in range(max(1, int(push_streams)))]
             # store_push = the operand (0 = A, 1 = B) whose planes the pack kernel itself stores into the
             # other consumers' buffers (NVLink stores) instead of the copy engines, or None
-            # push = "kernel": the planes travel by imd_push_ranges (a few CTAs beside the GEMM, NVLink
-            # stores, one launch per residue group that also sets the consumers' flag words);
-            # push = "copy": by the copy engines, one cudaMemcpyAsync per plane and flag
+            # push = "copy" (default): the planes travel by the copy engines, one cudaMemcpyAsync per
+            # plane and flag; push = "kernel": by imd_push_ranges (a few CTAs, NVLink stores, one launch
+            # per operand and residue group that also sets the consumers' flag words). Measured on 2 and
+            # 4 GPUs: the copy kernel's stores stall the GEMM that runs beside it (0 - 40 % of its
+            # normal progress), copy-engine transfers do not; more than one copy stream delays the
+            # first group (2.09 ms with one stream, 2.44 with two, 2.70 with four at 4 GPUs)
             if push not in ("kernel", "copy"):
                 raise ValueError("push must be 'kernel' or 'copy'")
             self.push, self.push_ctas = push, int(push_ctas)
