@@ -28,6 +28,22 @@ using Big = Wide<kBigLimbs>;
 // limb sum stays below 2^32), then normalised to `words` 32-bit words.
 constexpr int kCrtWords = 6;     // 32-bit words of the widest S (N P < 2^160, limbs up to 171 bits)
 constexpr int kCrtMaxLimbs = 9;
+
+// Constants of the CRT kernel's floating-point shortcut (dev::crt_fast). With 1 / p_l = rh_l + rl_l,
+// rh_l a multiple of 2^-46, the centred fraction f = sum_l y_l / p_l - Q (Q the nearest integer)
+// is fh + sl: fh = sum_l y_l rh_l - Q comes out exactly in binary64 (every partial sum is a
+// multiple of 2^-46 below 64), sl = sum_l y_l rl_l is tiny (below 2^-33) and rounded. The digits
+// enter as 256 + y_l (one shift and one mask build that double), and k0h, k0l take the 256 out
+// again. z = P f is then formed in double-double; `eabs` bounds its absolute error, rmax_hi is the
+// high word of a magnitude safely inside P / 2.
+struct CrtFast {
+  double rh[kMaxModuli], rl[kMaxModuli];
+  double k0h, k0l;
+  double Ph, Pl;       // P = Ph + Pl + (less than 2^-105 P)
+  double eabs;
+  int32_t rmax_hi;
+};
+
 struct CrtTables {
   int32_t N;
   int32_t nl, lw;                      // limbs and limb width: 20 bits for N <= 16, else 19
@@ -40,6 +56,7 @@ struct CrtTables {
   uint32_t M[kMaxModuli][kCrtMaxLimbs];  // limbs of P / p_l
   uint32_t P[kCrtWords];
   uint32_t H[kCrtWords];               // P / 2 - 1: the largest representable |z|
+  CrtFast fast;
 };
 
 // Constants of the residue emitter for one N (uniform across a warp: kernels take them by value
@@ -97,9 +114,56 @@ inline PlanConstants plan_constants(int N) {
   return c;
 }
 
+// 53 bits of x starting `skip` bits below its leading bit, as an exact double (0 when x has fewer).
+inline double wide_bits_as_double(const Big& x, int skip) {
+  const int B = wide_bitlen(x);
+  if (B <= skip) return 0.0;
+  const int low = B - skip - 53;  // position of the last bit taken
+  const Big sh = low >= 0 ? wide_shr(x, low) : wide_shl(x, -low);
+  const uint64_t m = (sh.w[0] | (static_cast<uint64_t>(sh.w[1]) << 32)) & ((uint64_t{1} << 53) - 1);
+  double v = static_cast<double>(m);  // exact: 53 bits
+  for (int i = 0; i < (low >= 0 ? low : -low); ++i) v = low >= 0 ? v * 2.0 : v * 0.5;
+  return v;
+}
+
+inline CrtFast crt_fast_tables(int N, const Big& P) {
+  CrtFast f{};
+  int64_t ksum = 0;
+  __int128 nsum = 0;  // sum_l n_l 2^64 / p_l, each term within one unit
+  for (int l = 0; l < N; ++l) {
+    const int64_t p = kModuli[l];
+    const int64_t k = ((int64_t{1} << 46) + p / 2) / p;
+    const int64_t n = (int64_t{1} << 46) - k * p;  // 1 / p = (k + n / p) 2^-46, |n| <= p / 2
+    f.rh[l] = static_cast<double>(k) * 0x1p-46;
+    f.rl[l] = static_cast<double>(n) / static_cast<double>(p) * 0x1p-46;
+    ksum += k;
+    nsum += (static_cast<__int128>(n) << 64) / p;
+  }
+  f.k0h = -static_cast<double>(ksum * 256) * 0x1p-46;                    // exact: below 2^52
+  f.k0l = -static_cast<double>(nsum) * 0x1p-64 * 256.0 * 0x1p-46;
+  f.Ph = wide_bits_as_double(P, 0);
+  f.Pl = wide_bits_as_double(P, 53);
+  // Error of fh + sl against the exact f. The partial sums of sl stay below maxpart, so each of
+  // its N fused multiply-adds errs by at most half an ulp of `ub`; the stored rl_l and k0l carry
+  // their own roundings. z adds the roundings of the double-double product.
+  const double maxpart = N * 767.0 * 0x1p-47;
+  double ub = 0x1p-60;
+  while (ub < maxpart) ub *= 2.0;
+  const double ef = N * ub * 0x1p-53 + N * 511.0 * 0x1p-100 + N * 256.0 * 0x1p-100 + N * 0x1p-102;
+  const double ex = ef + 4.0 * 0x1p-53 * (maxpart + 0x1p-50) + 0x1p-104;
+  f.eabs = 2.0 * f.Ph * ex;
+  const double rmax = f.Ph * (0.5 - 0x1p-20);
+  uint64_t bits;
+  static_assert(sizeof(bits) == sizeof(rmax), "binary64");
+  __builtin_memcpy(&bits, &rmax, 8);
+  f.rmax_hi = static_cast<int32_t>(bits >> 32);
+  return f;
+}
+
 inline CrtTables crt_tables(int N) {
   CrtTables t{};
   const PlanConstants c = plan_constants(N);
+  t.fast = crt_fast_tables(N, c.P);
   t.N = N;
   const Big NP = wide_mul_small(c.P, static_cast<uint32_t>(N));
   t.lw = N <= 16 ? 20 : 19;

@@ -75,6 +75,11 @@ IMD_API int imd_test_force_exact_shift(int on) {
   imd::g_hooks.force_exact_shift = on != 0;
   return 0;
 }
+/* 1: later calls run every output through the integer CRT (no FP64 shortcut). */
+IMD_API int imd_test_force_exact_crt(int on) {
+  imd::g_hooks.force_exact_crt = on != 0;
+  return 0;
+}
 /* The device error word, read and cleared (imd_device_error without the status). */
 IMD_API unsigned int imd_test_device_error(void) {
   unsigned int v = 0;

@@ -98,6 +98,7 @@ struct Hooks {
   int gemm_band_mb = 32;        // MB of operand A's tile rows the tile order keeps in L2
   int gemm_l2_hints = 5;        // eviction hints of the GEMM's operand loads (evict last on both)
   int force_exact_shift = 0;    // 1 = the scale step never takes its FP64 shortcut
+  int force_exact_crt = 0;      // 1 = the CRT step never takes its FP64 shortcut
 };
 const Hooks& hooks();
 // Phase boundary of a call (tags: 1 vectors + scale, 2 quantise, 3 GEMM, 4 CRT, 5 degenerate path,

@@ -9,6 +9,7 @@
 #include <cstdint>
 
 #include "carry.cuh"
+#include "common/crtfast.hpp"
 #include "common/modred.hpp"
 #include "common/wide.hpp"
 #include "kernels.hpp"
@@ -287,6 +288,17 @@ __device__ __forceinline__ bool crt(const CrtTables& t, const uint32_t* packed, 
   }
   return neg;
 }
+
+// Residue l of the thread's output x (byte x of packed[l]) as the double 256 + y: exponent 2^8, y
+// in the top eight bits of the fraction. One shift and one mask-or (x is a constant after unrolling).
+struct PackedDigit {
+  const uint32_t* packed;
+  __device__ __forceinline__ double operator()(int l, int x) const {
+    const uint32_t at12 = x == 0 ? packed[l] << 12 : x == 1 ? packed[l] << 4
+                        : x == 2 ? packed[l] >> 4 : packed[l] >> 12;
+    return __hiloint2double(static_cast<int>((at12 & 0x000FF000u) | 0x40700000u), 0);
+  }
+};
 
 // 64 bits of mag starting at bit position pos (pos >= 0).
 template <int LIMBS>

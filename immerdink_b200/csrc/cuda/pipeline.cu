@@ -234,6 +234,7 @@ struct CrtParams {
   int64_t m, n, n_hat, k, b;
   int32_t lg_fast;
   int32_t part;  // 0 all outputs, 1 emulated outputs only, 2 native-path outputs only
+  int32_t exact_only;  // verification: every output takes the integer path
   double alpha, beta;
   CrtTables t;
 };
@@ -250,89 +251,118 @@ __device__ __noinline__ double native_dot(const double* a, const double* b, cons
   return acc;
 }
 
-// One output of the thread's four: flagged rows / columns take the native FMA chain.
-template <int N, int LANE>
-__device__ __forceinline__ double crt_value(const CrtParams& p, const uint32_t* packed, int64_t lam,
-                                            int64_t i, int64_t j, int si, bool fa, int tau, bool fb) {
+// The integer path of one output (exact CRT on limbs, one rounding): taken by the few outputs whose
+// floating-point shortcut cannot vouch for its rounding. Out of line, and it reads its digits from
+// the planes again, so that nothing of it weighs on the registers of the common path.
+template <int N>
+__device__ __noinline__ double crt_exact(const CrtTables* t, const uint8_t* w, int64_t plane, int e) {
   constexpr int WORDS = dev::CrtShape<N>::kWords;
-  if (fa || fb)
-    return native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j],
-                      p.v.a_k, p.v.b_k, p.k);
-  uint32_t mag[WORDS];
-  const bool neg = dev::crt<N, LANE>(p.t, packed, mag);
-  return dev::round_scaled_fast<WORDS>(mag, neg, -(si + tau));
+  uint32_t y[N], mag[WORDS];
+#pragma unroll
+  for (int l = 0; l < N; ++l) y[l] = w[l * plane];
+  const bool neg = dev::crt<N, 0>(*t, y, mag);
+  return dev::round_scaled_fast<WORDS>(mag, neg, e);
 }
 
 // One thread = 4 consecutive columns of one row of one batch. Grid: x (with 2^lg_fast threads of a
-// CTA) covers the column quads of a row, y and the remaining threads stride over the rows.
+// CTA) covers the column quads of a row, y and the remaining threads stride over the rows of one
+// batch, z strides over the batches. Every output first goes through the floating-point shortcut
+// (straight-line code for the thread's four); the outputs it cannot vouch for and those of
+// flagged rows / columns (native FMA chain) are redone one by one afterwards.
+constexpr int kCrtCtasPerSm = 4;  // 64 registers: measured against 2, 3 and 5 CTAs per SM
 template <int N>
-__global__ void __launch_bounds__(kThreads, 3) k_crt(const __grid_constant__ CrtParams p) {
+__global__ void __launch_bounds__(kThreads, kCrtCtasPerSm) k_crt(const __grid_constant__ CrtParams p) {
   const int64_t quads = p.n_hat >> 2;
   const int F = 1 << p.lg_fast, per = kThreads >> p.lg_fast;
   const int64_t jq = static_cast<int64_t>(blockIdx.x) * F + (threadIdx.x & (F - 1));
   const int64_t j0 = jq << 2;
   if (jq >= quads || j0 >= p.n) return;
   const int64_t plane = p.b * p.m * p.n_hat;
-  const int64_t total_rows = p.b * p.m;
   const int64_t left = p.n - j0;  // >= 1
+  const unsigned inside = left > 3 ? 15u : (1u << left) - 1u;
   // the thread's four outputs are adjacent in C and 16-byte aligned relative to the row start?
   const int64_t c0 = p.v.c_col[j0];
   const bool adjacent = left > 3 && p.v.c_col[j0 + 3] == c0 + 3 && p.v.c_col[j0 + 1] == c0 + 1 &&
                         p.v.c_col[j0 + 2] == c0 + 2;
   const int64_t c1 = left > 1 ? p.v.c_col[j0 + 1] : 0, c2 = left > 2 ? p.v.c_col[j0 + 2] : 0,
                 c3 = left > 3 ? p.v.c_col[j0 + 3] : 0;
-  for (int64_t rho = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
-       rho < total_rows; rho += static_cast<int64_t>(gridDim.y) * per) {
-    int64_t lam = 0, i = rho;
-    if (p.b != 1) {
-      lam = rho / p.m;
-      i = rho - lam * p.m;
-    }
-    bool fa = p.fA[rho] != 0;
+  const int64_t row_step = static_cast<int64_t>(gridDim.y) * per;
+  for (int64_t lam = blockIdx.z; lam < p.b; lam += gridDim.z) {
     const int16_t* tau = p.tau + lam * p.n + j0;
     const uint8_t* fb = p.fB + lam * p.n + j0;
-    bool f0 = fb[0] != 0, f1 = left > 1 && fb[1] != 0, f2 = left > 2 && fb[2] != 0,
-         f3 = left > 3 && fb[3] != 0;
-    // part 0: every output. part 1: only the outputs of the emulated path (A and B are not read);
-    // part 2: only the outputs of the native path (flagged row or column).
-    bool w0 = true, w1 = true, w2 = true, w3 = true;
-    if (p.part != 0) {
-      const bool native = p.part == 2;
-      if (native && !(fa || f0 || f1 || f2 || f3)) continue;
-      w0 = (fa || f0) == native, w1 = (fa || f1) == native, w2 = (fa || f2) == native,
-      w3 = (fa || f3) == native;
-      if (!native) fa = f0 = f1 = f2 = f3 = false;  // skipped outputs: keep off the native path
-    }
-    const uint8_t* w = p.W + rho * p.n_hat + j0;
-    uint32_t packed[N];
-#pragma unroll
-    for (int l = 0; l < N; ++l) packed[l] = *reinterpret_cast<const uint32_t*>(w + l * plane);
-    const int si = p.sigma[rho];
-    double D0, D1 = 0.0, D2 = 0.0, D3 = 0.0;
-    D0 = crt_value<N, 0>(p, packed, lam, i, j0, si, fa, tau[0], f0);
-    if (left > 1) D1 = crt_value<N, 1>(p, packed, lam, i, j0 + 1, si, fa, tau[1], f1);
-    if (left > 2) D2 = crt_value<N, 2>(p, packed, lam, i, j0 + 2, si, fa, tau[2], f2);
-    if (left > 3) D3 = crt_value<N, 3>(p, packed, lam, i, j0 + 3, si, fa, tau[3], f3);
-    double* crow = p.C + p.v.c_bat[lam] + p.v.c_row[i];
-    double* c = crow + c0;
-    if (adjacent && w0 && w1 && w2 && w3 && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
-      double2* cv = reinterpret_cast<double2*>(c);
-      double2 lo = make_double2(0.0, 0.0), hi = lo;
-      if (p.beta != 0.0) {
-        lo = cv[0];
-        hi = cv[1];
+    const int t0 = tau[0], t1 = left > 1 ? tau[1] : 0, t2 = left > 2 ? tau[2] : 0,
+              t3 = left > 3 ? tau[3] : 0;
+    unsigned col_flags = fb[0] != 0 ? 1u : 0u;
+    if (left > 1 && fb[1] != 0) col_flags |= 2u;
+    if (left > 2 && fb[2] != 0) col_flags |= 4u;
+    if (left > 3 && fb[3] != 0) col_flags |= 8u;
+    double* cbat = p.C + p.v.c_bat[lam];
+    const int64_t i0 = static_cast<int64_t>(blockIdx.y) * per + (threadIdx.x >> p.lg_fast);
+    const uint8_t* w = p.W + (lam * p.m + i0) * p.n_hat + j0;
+    for (int64_t i = i0; i < p.m; i += row_step, w += row_step * p.n_hat) {
+      const int64_t rho = lam * p.m + i;
+      const unsigned fa = p.fA[rho];
+      // outputs of flagged rows / columns take the native path
+      unsigned native = (fa != 0 ? 15u : col_flags) & inside;
+      // part 0: every output. part 1: only the outputs of the emulated path (A and B are not
+      // read); part 2: only the outputs of the native path.
+      unsigned wanted = inside;
+      if (p.part == 1) wanted &= ~native, native = 0;
+      if (p.part == 2) {
+        wanted &= native;
+        if (wanted == 0) continue;
       }
-      lo.x = finish(D0, p.alpha, p.beta, &lo.x);
-      lo.y = finish(D1, p.alpha, p.beta, &lo.y);
-      hi.x = finish(D2, p.alpha, p.beta, &hi.x);
-      hi.y = finish(D3, p.alpha, p.beta, &hi.y);
-      cv[0] = lo;
-      cv[1] = hi;
-    } else {
-      if (w0) *c = finish(D0, p.alpha, p.beta, c);
-      if (left > 1 && w1) crow[c1] = finish(D1, p.alpha, p.beta, crow + c1);
-      if (left > 2 && w2) crow[c2] = finish(D2, p.alpha, p.beta, crow + c2);
-      if (left > 3 && w3) crow[c3] = finish(D3, p.alpha, p.beta, crow + c3);
+      uint32_t packed[N];
+#pragma unroll
+      for (int l = 0; l < N; ++l) packed[l] = *reinterpret_cast<const uint32_t*>(w + l * plane);
+      const int si = p.sigma[rho];
+      double D0, D1, D2, D3;
+      unsigned redo = 0;
+      {
+        // a zero the compiler cannot fold: with a known offset it holds all the constants of the
+        // sums in registers across the row loop and spills
+        int zero;
+        asm volatile("mov.u32 %0, 0;" : "=r"(zero));
+        double sh[4], sl[4];
+        crt_fast_sums<N, 4>(p.t.fast, dev::PackedDigit{packed}, zero, sh, sl);
+        if (!crt_fast_round(p.t.fast, sh[0], sl[0], -(si + t0), &D0)) redo |= 1u;
+        if (!crt_fast_round(p.t.fast, sh[1], sl[1], -(si + t1), &D1)) redo |= 2u;
+        if (!crt_fast_round(p.t.fast, sh[2], sl[2], -(si + t2), &D2)) redo |= 4u;
+        if (!crt_fast_round(p.t.fast, sh[3], sl[3], -(si + t3), &D3)) redo |= 8u;
+      }
+      if (p.exact_only) redo = 15u;
+      redo = (redo | native) & wanted;
+      if (redo) {
+        const double* arow = p.A + p.v.a_bat[lam] + p.v.a_row[i];
+        const double* bbat = p.B + p.v.b_bat[lam];
+#define IMD_REDO(x, D, tx)                                                                     \
+  if (redo & (1u << x))                                                                          \
+    D = (native & (1u << x)) ? native_dot(arow, bbat + p.v.b_col[j0 + x], p.v.a_k, p.v.b_k, p.k) \
+                             : crt_exact<N>(&p.t, w + x, plane, -(si + tx));
+        IMD_REDO(0, D0, t0) IMD_REDO(1, D1, t1) IMD_REDO(2, D2, t2) IMD_REDO(3, D3, t3)
+#undef IMD_REDO
+      }
+      double* crow = cbat + p.v.c_row[i];
+      double* c = crow + c0;
+      if (adjacent && wanted == 15u && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+        double2* cv = reinterpret_cast<double2*>(c);
+        double2 lo = make_double2(0.0, 0.0), hi = lo;
+        if (p.beta != 0.0) {
+          lo = cv[0];
+          hi = cv[1];
+        }
+        lo.x = finish(D0, p.alpha, p.beta, &lo.x);
+        lo.y = finish(D1, p.alpha, p.beta, &lo.y);
+        hi.x = finish(D2, p.alpha, p.beta, &hi.x);
+        hi.y = finish(D3, p.alpha, p.beta, &hi.y);
+        cv[0] = lo;
+        cv[1] = hi;
+      } else {
+        if (wanted & 1u) *c = finish(D0, p.alpha, p.beta, c);
+        if (wanted & 2u) crow[c1] = finish(D1, p.alpha, p.beta, crow + c1);
+        if (wanted & 4u) crow[c2] = finish(D2, p.alpha, p.beta, crow + c2);
+        if (wanted & 8u) crow[c3] = finish(D3, p.alpha, p.beta, crow + c3);
+      }
     }
   }
 }
@@ -719,14 +749,26 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   p.m = e.m, p.n = e.n, p.n_hat = e.n_hat, p.k = e.k, p.b = e.b;
   p.alpha = alpha, p.beta = beta;
   p.part = crt_part;
+  p.exact_only = hooks().force_exact_crt;
   p.t = plan.crt;
-  const int64_t quads = e.n_hat >> 2, rows_total = e.b * e.m;
+  const int64_t quads = e.n_hat >> 2;
   p.lg_fast = 0;
   while (p.lg_fast < 8 && (int64_t{1} << p.lg_fast) < quads) ++p.lg_fast;
   const int64_t Fq = int64_t{1} << p.lg_fast, perq = kThreads / Fq;
-  const int64_t gyq = (rows_total + perq - 1) / perq;
-  const dim3 grid(static_cast<unsigned int>((quads + Fq - 1) / Fq),
-                  static_cast<unsigned int>(gyq < 65535 ? gyq : 65535));
+  const int64_t gxq = (quads + Fq - 1) / Fq;
+  // A thread's set-up (its columns' shifts, flags and C offsets) is paid once and used for all the
+  // rows it walks: about twelve CTAs per SM in all, rows of one batch over y, batches over z.
+  const int64_t want_ctas = int64_t{12} * plan.sms;
+  int64_t gyq = (e.m + perq - 1) / perq;
+  const int64_t gy_cap = (want_ctas + gxq - 1) / gxq;
+  if (gyq > gy_cap) gyq = gy_cap;
+  if (gyq > 65535) gyq = 65535;
+  int64_t gzq = (want_ctas + gxq * gyq - 1) / (gxq * gyq);
+  if (gzq > e.b) gzq = e.b;
+  if (gzq > 65535) gzq = 65535;
+  if (gzq < 1) gzq = 1;
+  const dim3 grid(static_cast<unsigned int>(gxq), static_cast<unsigned int>(gyq),
+                  static_cast<unsigned int>(gzq));
   if (plan.crt.nl != dev::crt_limbs_of(e.N)) return IMD_STATUS_CUDA_ERROR;  // tables out of step
   switch (e.N) {
 #define IMD_CRT_CASE(n) case n: launch_crt<n>(p, grid, stream); break;
