@@ -80,6 +80,12 @@ IMD_API int imd_test_force_exact_crt(int on) {
   imd::g_hooks.force_exact_crt = on != 0;
   return 0;
 }
+/* 0: later calls run small contractions through the general kernel sequence (whose intermediate
+ * results the tests read from the workspace) instead of the one fused launch; 1: as in production. */
+IMD_API int imd_test_small_path(int on) {
+  imd::g_hooks.small_path = on != 0;
+  return 0;
+}
 /* The device error word, read and cleared (imd_device_error without the status). */
 IMD_API unsigned int imd_test_device_error(void) {
   unsigned int v = 0;

@@ -99,6 +99,7 @@ struct Hooks {
   int gemm_l2_hints = 5;        // eviction hints of the GEMM's operand loads (evict last on both)
   int force_exact_shift = 0;    // 1 = the scale step never takes its FP64 shortcut
   int force_exact_crt = 0;      // 1 = the CRT step never takes its FP64 shortcut
+  int small_path = 1;           // 0 = small contractions take the general kernel sequence too
 };
 const Hooks& hooks();
 // Phase boundary of a call (tags: 1 vectors + scale, 2 quantise, 3 GEMM, 4 CRT, 5 degenerate path,

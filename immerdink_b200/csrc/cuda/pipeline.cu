@@ -367,6 +367,12 @@ __global__ void __launch_bounds__(kThreads, kCrtCtasPerSm) k_crt(const __grid_co
   }
 }
 
+}  // namespace
+}  // namespace imd
+#include "small.cuh"
+namespace imd {
+namespace {
+
 template <int N>
 void launch_crt(const CrtParams& p, dim3 grid, cudaStream_t stream) {
   k_crt<N><<<grid, kThreads, 0, stream>>>(p);
@@ -499,7 +505,10 @@ GemmShape gemm_shape(const ExecPlan& e, const uint32_t* crt_q, int mod0, int mod
   return s;
 }
 
-// Plan time: the fused quantise launches may use up to kQStageMax units of dynamic shared memory.
+constexpr int kSmallSmemMax = 200 * 1024;
+
+// Plan time: the fused quantise launches may use up to kQStageMax units of dynamic shared memory,
+// the small-contraction kernel up to kSmallSmemMax bytes.
 imd_status_t quantize_setup() {
   const int bytes = kQStageMax * kQStageBytes;
   const bool ok =
@@ -508,6 +517,11 @@ imd_status_t quantize_setup() {
       cudaFuncSetAttribute(k_quantize<3, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess &&
       cudaFuncSetAttribute(k_quantize<3, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
   if (!ok) cudaGetLastError();
+  if (ok && cudaFuncSetAttribute(k_small, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmallSmemMax) != cudaSuccess) {
+    cudaGetLastError();
+    return IMD_STATUS_CUDA_ERROR;
+  }
   return ok ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
 }
 
@@ -690,6 +704,32 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
   }
   uint8_t* W = reinterpret_cast<uint8_t*>(region(IMD_REGION_W));
   const OperandView ov[2] = {operand_view(e, v, 0, A), operand_view(e, v, 1, B)};
+
+  if (e.small() && part == 0 && hooks().small_path) {
+    SmallParams sp{};
+    sp.A = A, sp.B = B, sp.C = C;
+    sp.v = v;
+    sp.m = e.m, sp.n = e.n, sp.k = e.k, sp.b = e.b;
+    sp.kh = static_cast<int32_t>((e.k + 31) / 32 * 32);
+    sp.N = e.N, sp.trunc = e.trunc ? 1 : 0, sp.lhs_shift = e.lhs_shift;
+    sp.force_exact_shift = hooks().force_exact_shift, sp.exact_crt = hooks().force_exact_crt;
+    sp.rhs = e.rhs, sp.fast = e.fast;
+    sp.alpha = alpha, sp.beta = beta;
+    sp.sigma_a = const_cast<int16_t*>(sX[0]), sp.sigma_b = const_cast<int16_t*>(sX[1]);
+    sp.flag_a = const_cast<uint8_t*>(fX[0]), sp.flag_b = const_cast<uint8_t*>(fX[1]);
+    sp.t = plan.res, sp.crt = plan.crt;
+    // as many moduli per pass as the residues' share of shared memory holds
+    const int64_t fixed = static_cast<int64_t>(small_smem_bytes(sp.kh, 0, e.N));
+    const int64_t per_modulus = static_cast<int64_t>(kSmRows) * (sp.kh + kSmPad);
+    int64_t group = (kSmallSmemMax - fixed) / per_modulus;
+    if (group > e.N) group = e.N;
+    if (group < 1) return IMD_STATUS_CUDA_ERROR;  // cannot happen: k <= 128 leaves room for 8 moduli
+    sp.group = static_cast<int32_t>(group);
+    const int64_t tiles = ((e.m + kSmTM - 1) / kSmTM) * ((e.n + kSmTN - 1) / kSmTN) * e.b;
+    k_small<<<static_cast<unsigned int>(tiles), kSmThreads, small_smem_bytes(sp.kh, sp.group, e.N), stream>>>(sp);
+    phase_mark(4, stream);
+    return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
+  }
 
   PackDests dest[2];
   // Parts (imd_contract_packed_part): 0 everything; 1 everything but the native-path outputs;

@@ -95,6 +95,7 @@ imd_status_t lowering_impl(const imd_tensor_t* A, const imd_tensor_t* B, const i
     }
     e.vec_resident = an.options.vec_mode == IMD_VEC_RESIDENT && e.path != imd::Path::kNoop;
     r.kernel_launches = imd::plan_kernel_launches(e);
+    r.fused = e.small() ? 1 : 0;
     r.sm_count = sms_in > 0 ? sms_in : imd::kDefaultSms;
     r.k4_config = IMD_K4_128x256;
     if (plan_st != IMD_STATUS_SUCCESS) return plan_st;

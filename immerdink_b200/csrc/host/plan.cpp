@@ -183,6 +183,7 @@ int64_t plan_kernel_launches(const ExecPlan& e) {
   if (e.path == Path::kNoop) return 0;
   const int64_t vec = e.vec_resident ? 0 : 1;
   if (!e.emulated()) return vec + 1;  // native FP64 kernel, or C <- beta C
+  if (e.small()) return vec + 1;      // everything in one fused launch
   const int64_t groups = (e.N + e.g - 1) / e.g;
   // vectors; per group one quantise launch per operand and the GEMM launches; one CRT launch.
   // an in-line operand that is contiguous along its rows needs its own scale launch; the others

@@ -204,6 +204,16 @@ class RankContraction:
     (imd_wait_flags: a wait that runs out sets the device error word, the stream moves on); one
     all-reduce per step remains, before the slabs are overwritten.
 
+    "pieces": the FP64 pieces themselves travel (8 bytes per entry instead of N), one contiguous
+    peer copy per piece and consumer on the copy engines, announced by flag words; every consumer
+    quantises the pieces of its slabs as they arrive (imd_pack_scatter on the rows of a piece: its
+    own pieces first, while the others are on their way), then runs the whole contraction from
+    the packed slabs in the plan's own residue groups. A rank repeats the quantisation of the
+    other consumers of its slabs, but no GEMM launch waits for a transfer:
+
+        main   barrier | pack own B, own A | piece in, pack | piece in, pack ... | GEMMs | CRT | native path
+        side           | push own pieces to the other consumers |
+
     "fp64": the slabs are all-gathered as FP64 (NCCL, side stream), A is packed as soon as its
     slab is complete and while B's is still arriving, B is quantised in line.
 
@@ -233,7 +243,9 @@ class RankContraction:
         lays = (la_, lb_, lc)
         specs = [_dev.pack_spec(self.spec, *lays, operand=x, N=N, g=g, rounding=rounding, lib=lib)
                  for x in (0, 1)]
-        if self.exchange == "residues":
+        if self.exchange not in ("residues", "pieces", "fp64"):
+            raise ValueError("exchange must be 'residues', 'pieces' or 'fp64'")
+        if self.exchange in ("residues", "pieces"):
             pieces = [piece_pack_spec(part, x, specs[x]) for x in (0, 1)]
             if any(p is None for p in pieces):
                 self.exchange = "fp64"      # the piece index is not the slowest row mode
@@ -419,6 +431,8 @@ class RankContraction:
         torch = self._torch
         main = torch.cuda.current_stream()
         cols, rows = self.groups
+        if self.exchange == "pieces":
+            return self._step_pieces(shard_a, shard_b, C, alpha, beta)
         if self.exchange == "fp64":
             self.side.wait_event(main.record_event())
             with torch.cuda.stream(self.side):
@@ -603,6 +617,87 @@ class RankContraction:
         self._mark("end", main)
         return C
 
+    def _step_pieces(self, shard_a, shard_b, C, alpha, beta):
+        """The step of the "pieces" exchange (see the class text)."""
+        from .device import copy_if_flagged as _dev_copy_if, wait_flags as _dev_wait
+        torch, rt = self._torch, self._rt
+        main = torch.cuda.current_stream()
+        s = main.cuda_stream
+        if int(self._err_host[0]) != 0:
+            word = self.device_error()        # synchronises and clears
+            self._err_host[0] = 0
+            raise RuntimeError(f"piece exchange: device error word {word:#x} after an earlier step (bit 2: a "
+                               "producer's piece did not arrive within the bounded wait); the tiles of that "
+                               "step and of those enqueued since are not valid: repeat them")
+        shards = (shard_a, shard_b)
+        for x in (0, 1):
+            if (tuple(shards[x].shape) != tuple(self.part.shard_shape(x)) or not shards[x].is_contiguous()
+                    or shards[x].dtype != torch.float64):
+                raise ValueError("the rank's pieces must be dense FP64 arrays of Partition.shard_shape")
+        if tuple(C.shape) != tuple(self.tile_shape) or not C.is_contiguous() or C.dtype != torch.float64:
+            raise ValueError("C must be the rank's dense FP64 tile")
+        kind = rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice
+        push = self.push_streams[0]
+        self.step = self.step % 65535 + 1
+        tick = self.step
+        slot = _SLOTS - 1
+        pieces_of = (self.part.pieces_b, self.part.pieces_a)     # pieces of the slab of A, of B
+        piece_bytes = [shards[x].numel() * 8 for x in (0, 1)]
+
+        def copy(dst, src, nbytes):
+            err, = rt.cudaMemcpyAsync(dst, src, nbytes, kind, push.cuda_stream)
+            if err != rt.cudaError_t.cudaSuccess:
+                raise RuntimeError(f"cudaMemcpyAsync to a peer: {err}")
+
+        def word(x, position):
+            return 4 * ((x * _POSITIONS + position) * _SLOTS + slot)
+
+        self._mark("begin", main)
+        self._barrier()                       # every rank is done with the previous step's slabs
+        self._mark("all ranks in", main)
+        push.wait_event(main.record_event())
+        # the slab with more consumers first; every producer serves the consumer after itself first
+        order = (1, 0) if self.part.pb > self.part.pa else (0, 1)
+        for x in order:
+            for j in self.push_order[x]:
+                copy(self.fp64_dests[x][1 + j] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(),
+                     piece_bytes[x])
+                copy(self.flag_dests[x][j] + word(x, self.pos[x]), self.values.data_ptr() + 4 * tick, 4)
+        sent = push.record_event()
+        self._mark("pushed", push)
+
+        def pack(x, src, position):
+            rp = self.piece[x].layout["r"]
+            self.piece[x].scatter_ptr(src, self.slab_rows[x], position * rp, self.dests[x][:1],
+                                      self.slab[x].pack_bytes, self.pack_ws[x].data_ptr(),
+                                      self.pack_ws[x].numel(), s)
+
+        for x in order:                       # own pieces: nothing to wait for
+            pack(x, shards[x].data_ptr(), self.pos[x])
+        self._mark("packed own", main)
+        for x in order:                       # the others in the order in which they arrive here
+            n = pieces_of[x]
+            for t in range(n - 1):
+                position = (self.pos[x] - 1 - t) % n
+                _dev_wait([self.flags + word(x, position)], tick, stream=s, lib=self.lib)
+                pack(x, self.fp64_dests[x][0] + position * piece_bytes[x], position)
+        self._mark("packed all", main)
+        # the own pieces at their place in the own FP64 slabs: only the native path of flagged rows
+        # reads them, so they are copied only if a row flag of the slabs is set
+        rows = [(self.dests[x][0] + self.slab[x].layout["flag"][0],
+                 self.slab[x].layout["b"] * self.slab_rows[x]) for x in (0, 1)]
+        own = [(self.fp64_dests[x][0] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(), piece_bytes[x])
+               for x in (0, 1)]
+        _dev_copy_if(rows, own, stream=s, lib=self.lib)
+        main.wait_event(sent)                 # the shards may change once the step's work is done
+        self.plan.contract_ptr(alpha, self.A.data_ptr(), self.B.data_ptr(), beta, C.data_ptr(),
+                               self.ws.data_ptr(), self.ws.numel(), s, packed=tuple(self.packed))
+        st = self.lib.lib.imd_device_error_peek(self._err_host.data_ptr(), s)
+        if st:
+            raise RuntimeError(f"imd_device_error_peek: status {st}")
+        self._mark("end", main)
+        return C
+
     def device_error(self):
         """Reads and clears the device error word (synchronises the device): nonzero when a
         bounded wait gave up, e.g. bit 2 (4) when a producer's planes did not arrive within about
@@ -617,7 +712,7 @@ class RankContraction:
         self.plan.close()
         for pk in ([self.pack] if self.exchange == "fp64" else self.slab + self.piece):
             pk.close()
-        if self.exchange == "residues" and getattr(self, "_owned", None):
+        if self.exchange in ("residues", "pieces") and getattr(self, "_owned", None):
             self._torch.cuda.synchronize()
             for ptr in self._opened:
                 self._rt.cudaIpcCloseMemHandle(ptr)

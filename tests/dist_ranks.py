@@ -51,7 +51,8 @@ def main():
     variants = [dict(exchange="residues", push="kernel"), dict(exchange="residues", push="kernel", push_ctas=4),
                 dict(exchange="residues", push="copy"), dict(exchange="residues", push="copy", store_push=0),
                 dict(exchange="residues", push="kernel", store_push=1),
-                dict(exchange="residues", push="copy", sync="barrier"), dict(exchange="fp64")]
+                dict(exchange="residues", push="copy", sync="barrier"), dict(exchange="fp64"),
+                dict(exchange="pieces")]
     for kw in variants:
         for g in (5, 14):
             rc = idist.RankContraction(part, N=14, g=g, dist=dist, groups=groups, **kw)

@@ -50,12 +50,15 @@ class Workspace:
 
 
 def run_descs(descs, bufs, bases, alpha, beta, N, g=0, rounding="RN", mode="EMULATE",
-              vec_mode="GENERATE", reference_gemm=False, want_ws=False, gemm_variant=0):
+              vec_mode="GENERATE", reference_gemm=False, want_ws=False, gemm_variant=0, small=None):
     """imd_plan_create + imd_contract on flat float64 buffers with raw descriptors. Returns the
-    whole C buffer (numpy) and, optionally, (plan, workspace)."""
+    whole C buffer (numpy) and, optionally, (plan, workspace). small: False keeps small
+    contractions on the general kernel sequence (always so when the workspace is wanted back:
+    the one fused launch leaves no residue or product planes there); None / True: as in production."""
     L = lib()
     L.lib.imd_test_use_reference_gemm(1 if reference_gemm else 0)
     L.lib.imd_test_gemm_variant(gemm_variant)
+    L.lib.imd_test_small_path(0 if (small is False or want_ws or reference_gemm or gemm_variant) else 1)
     try:
         plan = imd.Plan.from_descs(*descs, N=N, g=g, rounding=rounding, mode=mode, vec_mode=vec_mode)
         dA, dB, dC = (dev_f64(b) if b is not None else None for b in bufs)
@@ -71,6 +74,7 @@ def run_descs(descs, bufs, bases, alpha, beta, N, g=0, rounding="RN", mode="EMUL
     finally:
         L.lib.imd_test_use_reference_gemm(0)
         L.lib.imd_test_gemm_variant(0)
+        L.lib.imd_test_small_path(1)
     if want_ws:
         return out, plan, ws
     plan.close()

@@ -8,7 +8,7 @@ from golden_util import same_bits
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("exchange", ["fp64", "residues"])
+@pytest.mark.parametrize("exchange", ["fp64", "residues", "pieces"])
 def test_rank_contraction_world_1_equals_plain_call(exchange):
     import torch
     import immerdink_b200 as imd
