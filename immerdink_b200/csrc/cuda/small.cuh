@@ -1,11 +1,12 @@
 // Small contractions in one launch: shift, quantise, residues, int8 products, CRT and output of a
-// 32 x 64 tile of C inside one CTA, for k <= 128. At such sizes the general sequence (vectors,
+// 32 x 32 tile of C inside one CTA of 16 warps, for k <= 128. At such sizes the general sequence (vectors,
 // quantise A, quantise B, GEMM, CRT) is bound by its launches and by the round trips of tiny
 // intermediates through HBM. Every CTA scales and quantises the rows of A and the columns of B of
 // its own tile (other tiles repeat some of that work, which is cheap here), keeps the residues in
-// shared memory, multiplies them with mma.sync (m16n8k32, int8), reduces every product mod p_l and
-// folds the digit straight into the two FP64 sums of the CRT shortcut; digits are also kept in
-// shared memory for the outputs that need the integer CRT. The arithmetic is that of the general
+// shared memory, multiplies them with mma.sync (m16n8k32, int8; a warp takes a quarter of the tile
+// and every fourth modulus), reduces every product mod p_l into a digit in shared memory, and
+// every thread then runs the CRT of two outputs: the FP64 shortcut over the digits in the order
+// of the moduli, the integer CRT where the shortcut cannot vouch. The arithmetic is that of the general
 // path, function by function (numerics.cuh, modred.hpp, crtfast.hpp): results are bit-identical.
 //
 // Counterpart in the reference: the fused small-shape path of src/contract.cu:800-926 (KF) and its
@@ -19,9 +20,10 @@
 namespace imd {
 namespace {
 
-constexpr int kSmThreads = 256;
-constexpr int kSmTM = 32, kSmTN = 64, kSmRows = kSmTM + kSmTN;
+constexpr int kSmThreads = 512;  // measured on 64 x 32 x 48 . 48 x 40: 256 / 512 / 1024 threads 46 / 34 / 32 us
+constexpr int kSmTM = 32, kSmTN = 32, kSmRows = kSmTM + kSmTN;
 constexpr int kSmKMax = 128;
+constexpr int64_t kSmDead = INT64_MIN;
 constexpr int kSmPad = 16;  // bytes added to a residue row: fragment loads of 8 rows hit 8 banks
 
 struct SmallParams {
@@ -46,38 +48,41 @@ inline size_t small_smem_bytes(int kh, int group, int N) {
          static_cast<size_t>(N) * kSmTM * kSmTN;
 }
 
-// The shift and flag of one row held by a warp (lane x has entries x, x + 32, ... as bit patterns),
-// exactly as the quantise kernel decides them: FP64 shortcut, else exact 128-bit sum of squares.
-__device__ __forceinline__ void small_row_shift(const SmallParams& p, const uint64_t (&raw)[4], int cnt,
-                                                int* sigma_out, bool* flag_out) {
+// The shift and flag of one row, decided by eight adjacent lanes (lane x of the eight reads entries
+// x, x + 8, ... of the row's bit patterns in shared memory; four rows per warp at a time), exactly
+// as the quantise kernel decides them: FP64 shortcut, else exact 128-bit sum of squares. All 32
+// lanes call it together; the shuffles stay inside a group of eight.
+__device__ __forceinline__ void small_row_shift(const SmallParams& p, const uint64_t* row, int l8,
+                                                bool live, int* sigma_out, bool* flag_out) {
   uint32_t mx = 0;
   double acc = 0.0;
-  for (int c = 0; c < cnt; ++c) {
-    mx = max(mx, static_cast<uint32_t>(raw[c] >> 32) & 0x7FFFFFFFu);
-    const double x = __longlong_as_double(static_cast<long long>(raw[c]));
+  for (int h = l8; h < p.kh; h += 8) {
+    const uint64_t u = row[h];
+    mx = max(mx, static_cast<uint32_t>(u >> 32) & 0x7FFFFFFFu);
+    const double x = __longlong_as_double(static_cast<long long>(u));
     acc = __fma_rn(x, x, acc);
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
+  for (int o = 4; o > 0; o >>= 1) {
     mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
     acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
   }
   int sg = 0;
-  if (!p.force_exact_shift && dev::fast_shift(mx, acc, p.fast, p.lhs_shift, &sg)) {
-    *sigma_out = sg;
-    *flag_out = false;
-    return;
-  }
+  // rows outside the tensor (all zero) need no decision
+  const bool quick = !live || (!p.force_exact_shift && dev::fast_shift(mx, acc, p.fast, p.lhs_shift, &sg));
+  *sigma_out = sg;
+  *flag_out = false;
+  if (__all_sync(0xFFFFFFFFu, quick)) return;
   int g = 0;  // bit 30: a non-finite entry; low bits: gamma + 2048 (0: no finite nonzero entry)
-  for (int c = 0; c < cnt; ++c) {
+  for (int h = l8; h < p.kh; h += 8) {
     uint64_t M;
     int E;
-    const int kind = dev::decompose(raw[c], &M, &E);
+    const int kind = dev::decompose(row[h], &M, &E);
     if (kind < 0) g |= 1 << 30;
     else if (kind > 0) g = (g & (1 << 30)) | max(g & 0xFFFF, E + 52 + 2048);
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
+  for (int o = 4; o > 0; o >>= 1) {
     const int other = __shfl_xor_sync(0xFFFFFFFFu, g, o);
     g = ((g | other) & (1 << 30)) | max(g & 0xFFFF, other & 0xFFFF);
   }
@@ -85,10 +90,10 @@ __device__ __forceinline__ void small_row_shift(const SmallParams& p, const uint
   const int gamma = (g & 0xFFFF) - 2048;
   uint64_t hi = 0, lo = 0;
   if (any)
-    for (int c = 0; c < cnt; ++c) {
+    for (int h = l8; h < p.kh; h += 8) {
       uint64_t M;
       int E;
-      if (dev::decompose(raw[c], &M, &E) == 1) {
+      if (dev::decompose(row[h], &M, &E) == 1) {
         uint64_t th, tl;
         dev::square_term(M, E, gamma, &th, &tl);
         lo += tl;
@@ -96,13 +101,15 @@ __device__ __forceinline__ void small_row_shift(const SmallParams& p, const uint
       }
     }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
+  for (int o = 4; o > 0; o >>= 1) {
     const uint64_t oh = __shfl_xor_sync(0xFFFFFFFFu, hi, o), ol = __shfl_xor_sync(0xFFFFFFFFu, lo, o);
     lo += ol;
     hi += oh + (lo < ol ? 1 : 0);
   }
-  *sigma_out = any ? dev::shift_from_sum(hi, lo, p.lhs_shift, p.rhs, gamma) : 0;
-  *flag_out = ((g >> 30) & 1) != 0;
+  if (!quick) {
+    *sigma_out = any ? dev::shift_from_sum(hi, lo, p.lhs_shift, p.rhs, gamma) : 0;
+    *flag_out = ((g >> 30) & 1) != 0;
+  }
 }
 
 // The integer CRT of one output from digits `plane` bytes apart (any N; the instances are those of
@@ -146,51 +153,59 @@ __global__ void __launch_bounds__(kSmThreads) k_small(const __grid_constant__ Sm
     s_pm[tid][4] = p.crt.q[tid];
   }
   // ---- the tile's rows of A and columns of B: values, shifts, flags ----
-  // row r < TM: row i0 + r of A; row TM + c: column j0 + c of B; rows outside the tensor are zero
-  const int per_lane = p.kh >> 5;  // <= 4
-  for (int r = warp; r < kSmRows; r += kSmThreads / 32) {
-    const bool is_a = r < kSmTM;
-    const int64_t idx = is_a ? i0 + r : j0 + (r - kSmTM);
-    const bool live = idx < (is_a ? p.m : p.n);
-    const double* base = is_a ? p.A + p.v.a_bat[lam] : p.B + p.v.b_bat[lam];
-    if (live) base += is_a ? p.v.a_row[idx] : p.v.b_col[idx];
-    const int64_t* kv = is_a ? p.v.a_k : p.v.b_k;
-    uint64_t raw[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int h = lane + 32 * c;
-      if (c < per_lane) {
-        if (live && h < p.k) raw[c] = static_cast<uint64_t>(__double_as_longlong(base[kv[h]]));
-        s_raw[static_cast<size_t>(r) * p.kh + h] = raw[c];
-      }
-    }
-    int sg = 0;
-    bool fl = false;
-    if (live) small_row_shift(p, raw, per_lane, &sg, &fl);
-    if (lane == 0) {
-      s_sigma[r] = sg;
-      s_flag[r] = fl ? 1 : 0;
-      if (live && is_a && tn == 0) {
-        p.sigma_a[lam * p.m + idx] = static_cast<int16_t>(sg);
-        p.flag_a[lam * p.m + idx] = fl ? 1 : 0;
-      }
-      if (live && !is_a && tm == 0) {
-        p.sigma_b[lam * p.n + idx] = static_cast<int16_t>(sg);
-        p.flag_b[lam * p.n + idx] = fl ? 1 : 0;
+  // row r < TM: row i0 + r of A; row TM + c: column j0 + c of B; rows outside the tensor are zero.
+  // All loads of the tile are issued together (one row offset per row first), then eight lanes
+  // decide the shift of a row.
+  __shared__ int64_t s_off[kSmRows];
+  if (tid < kSmRows) {
+    const bool is_a = tid < kSmTM;
+    const int64_t idx = is_a ? i0 + tid : j0 + (tid - kSmTM);
+    int64_t off = kSmDead;  // offsets may be negative (negative strides): a value no row can have
+    if (idx < (is_a ? p.m : p.n)) off = is_a ? p.v.a_bat[lam] + p.v.a_row[idx] : p.v.b_bat[lam] + p.v.b_col[idx];
+    s_off[tid] = off;
+  }
+  __syncthreads();
+  for (int e = tid; e < kSmRows * p.kh; e += kSmThreads) {
+    const int r = e / p.kh, h = e - r * p.kh;
+    const int64_t off = s_off[r];
+    uint64_t bits = 0;
+    if (off != kSmDead && h < p.k)
+      bits = static_cast<uint64_t>(__double_as_longlong(
+          r < kSmTM ? p.A[off + p.v.a_k[h]] : p.B[off + p.v.b_k[h]]));
+    s_raw[e] = bits;
+  }
+  __syncthreads();
+  {
+    const int l8 = lane & 7;
+    for (int r = 4 * warp + (lane >> 3); r < kSmRows; r += 4 * (kSmThreads / 32)) {
+      int sg = 0;
+      bool fl = false;
+      const bool live = s_off[r] != kSmDead;
+      small_row_shift(p, s_raw + static_cast<size_t>(r) * p.kh, l8, live, &sg, &fl);
+      const bool is_a = r < kSmTM;
+      const int64_t idx = is_a ? i0 + r : j0 + (r - kSmTM);
+      if (l8 == 0) {
+        s_sigma[r] = live ? sg : 0;
+        s_flag[r] = live && fl ? 1 : 0;
+        if (live && is_a && tn == 0) {
+          p.sigma_a[lam * p.m + idx] = static_cast<int16_t>(sg);
+          p.flag_a[lam * p.m + idx] = fl ? 1 : 0;
+        }
+        if (live && !is_a && tm == 0) {
+          p.sigma_b[lam * p.n + idx] = static_cast<int16_t>(sg);
+          p.flag_b[lam * p.n + idx] = fl ? 1 : 0;
+        }
       }
     }
   }
   __syncthreads();
 
   // ---- per group of moduli: residues into shared memory, products, digits ----
-  // warp tile: 16 rows x 16 columns (two n-tiles of the mma); this thread's outputs: rows g8 and
-  // g8 + 8, columns 2 t4, 2 t4 + 1 of either n-tile
+  // warp w: quarter w & 3 of the tile (16 rows x 16 columns: two n-tiles of the mma) and the moduli
+  // w >> 2, w >> 2 + 4, ... of the group; a thread's accumulators: rows g8 and g8 + 8, columns
+  // 2 t4, 2 t4 + 1 of either n-tile
   const int g8 = lane >> 2, t4 = lane & 3;
-  const int wr = 16 * (warp & 1), wc = 16 * (warp >> 1);
-  double sh[8], sl[8];
-#pragma unroll
-  for (int x = 0; x < 8; ++x) sh[x] = p.crt.fast.k0h, sl[x] = p.crt.fast.k0l;
-
+  const int wr = 16 * (warp & 1), wc = 16 * ((warp >> 1) & 1);
   for (int l0 = 0; l0 < p.N; l0 += p.group) {
     const int mods = min(p.group, p.N - l0);
     for (int e = tid; e < kSmRows * p.kh; e += kSmThreads) {
@@ -215,7 +230,7 @@ __global__ void __launch_bounds__(kSmThreads) k_small(const __grid_constant__ Sm
       }
     }
     __syncthreads();
-    for (int l = 0; l < mods; ++l) {
+    for (int l = warp >> 2; l < mods; l += kSmThreads / 128) {
       const int8_t* ra = s_res + (static_cast<size_t>(l) * kSmRows + wr) * pitch;
       const int8_t* rb = s_res + (static_cast<size_t>(l) * kSmRows + kSmTM + wc) * pitch;
       int acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
@@ -238,7 +253,6 @@ __global__ void __launch_bounds__(kSmThreads) k_small(const __grid_constant__ Sm
       const int lg = l0 + l;
       const uint32_t pm = s_pm[lg][0], magic = s_pm[lg][1], magic_up = s_pm[lg][2], bias = s_pm[lg][3],
                      q = s_pm[lg][4];
-      const double rh = p.crt.fast.rh[lg], rl = p.crt.fast.rl[lg];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -246,34 +260,41 @@ __global__ void __launch_bounds__(kSmThreads) k_small(const __grid_constant__ Sm
           const uint32_t y = mod_epilogue(static_cast<uint32_t>(acc[nt][x]), pm, magic, magic_up, bias, q);
           const int row = wr + g8 + 8 * (x >> 1), colx = wc + 8 * nt + 2 * t4 + (x & 1);
           s_w[(static_cast<size_t>(lg) * kSmTM + row) * kSmTN + colx] = static_cast<uint8_t>(y);
-          const double d = __hiloint2double(static_cast<int>(0x40700000u | (y << 12)), 0);  // 256 + y
-          sh[4 * nt + x] = __fma_rn(d, rh, sh[4 * nt + x]);
-          sl[4 * nt + x] = __fma_rn(d, rl, sl[4 * nt + x]);
         }
     }
-    __syncthreads();  // the next group overwrites the residues
+    __syncthreads();  // the next group overwrites the residues; the digits are complete after the last
   }
 
-  // ---- CRT, alpha / beta, output ----
+  // ---- CRT, alpha / beta, output: adjacent outputs of a row per thread ----
+  constexpr int kPer = kSmTM * kSmTN / kSmThreads;
   const int64_t plane = static_cast<int64_t>(kSmTM) * kSmTN;
+  const int row = tid * kPer / kSmTN;
+  const int64_t i = i0 + row;
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int row = wr + g8 + 8 * (x >> 1), colx = wc + 8 * nt + 2 * t4 + (x & 1);
-      const int64_t i = i0 + row, j = j0 + colx;
-      if (i >= p.m || j >= p.n) continue;
-      const int e = -(s_sigma[row] + s_sigma[kSmTM + colx]);
-      double D;
-      if (s_flag[row] || s_flag[kSmTM + colx]) {
-        D = native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j], p.v.a_k,
-                       p.v.b_k, p.k);
-      } else if (p.exact_crt || !crt_fast_round(p.crt.fast, sh[4 * nt + x], sl[4 * nt + x], e, &D)) {
-        D = small_crt_exact(&p.crt, s_w + static_cast<size_t>(row) * kSmTN + colx, plane, e);
+  for (int x = 0; x < kPer; ++x) {
+    const int colx = tid * kPer % kSmTN + x;
+    const int64_t j = j0 + colx;
+    if (i >= p.m || j >= p.n) continue;
+    const uint8_t* digits = s_w + static_cast<size_t>(row) * kSmTN + colx;
+    const int e = -(s_sigma[row] + s_sigma[kSmTM + colx]);
+    double D;
+    if (s_flag[row] || s_flag[kSmTM + colx]) {
+      D = native_dot(p.A + p.v.a_bat[lam] + p.v.a_row[i], p.B + p.v.b_bat[lam] + p.v.b_col[j], p.v.a_k,
+                     p.v.b_k, p.k);
+    } else {
+      double sh = p.crt.fast.k0h, sl = p.crt.fast.k0l;
+      for (int l = 0; l < p.N; ++l) {
+        const uint32_t y = digits[l * plane];
+        const double d = __hiloint2double(static_cast<int>(0x40700000u | (y << 12)), 0);  // 256 + y
+        sh = __fma_rn(d, p.crt.fast.rh[l], sh);
+        sl = __fma_rn(d, p.crt.fast.rl[l], sl);
       }
-      double* c = p.C + p.v.c_bat[lam] + p.v.c_row[i] + p.v.c_col[j];
-      *c = finish(D, p.alpha, p.beta, c);
+      if (p.exact_crt || !crt_fast_round(p.crt.fast, sh, sl, e, &D))
+        D = small_crt_exact(&p.crt, digits, plane, e);
     }
+    double* c = p.C + p.v.c_bat[lam] + p.v.c_row[i] + p.v.c_col[j];
+    *c = finish(D, p.alpha, p.beta, c);
+  }
 }
 
 }  // namespace

@@ -82,10 +82,10 @@ struct ExecPlan {
   ModeTable modes;
   bool emulated() const { return path == Path::kGemm && k >= 2; }
   // Small contractions take one fused launch (k_small): short rows and at most 256 tiles of
-  // 32 x 64 outputs, no packed operand. The same test decides the lowering's launch count.
+  // 32 x 32 outputs, no packed operand. The same test decides the lowering's launch count.
   bool small() const {
     if (!emulated() || packed != 0 || k > 128) return false;
-    const int64_t tiles = ((m + 31) / 32) * ((n + 63) / 64);
+    const int64_t tiles = ((m + 31) / 32) * ((n + 31) / 32);
     return tiles <= 256 && b <= 256 && tiles * b <= 256;
   }
 };

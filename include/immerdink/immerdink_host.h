@@ -112,7 +112,7 @@ enum { IMD_DISPATCH_NOOP = 0, IMD_DISPATCH_EMULATE = 1, IMD_DISPATCH_DIRECT = 2,
  * describe THIS engine: n_hat = ceil(n)_16; k_hat = ceil(k)_A with A = k_align (64 iff
  * k > 96 else 16); gemm_launches = residue groups x K chunks (one batched tcgen05 launch
  * each); kernel_launches = every launch of one call; fused = 1 when the call is one fused
- * launch (k <= 128, no packed operand and at most 256 tiles of 32 x 64 outputs over all batches:
+ * launch (k <= 128, no packed operand and at most 256 tiles of 32 x 32 outputs over all batches:
  * shifts, residues, int8 products and CRT inside one CTA per tile; kernel_launches is then 1,
  * plus the vectors' launch), fused_large is 0 (in the general sequence the quantise kernel is
  * always one fused scale+pack launch per operand and group); k4_config is
