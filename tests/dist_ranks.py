@@ -39,35 +39,42 @@ def main():
     imd.contract(spec, dA, dB, full, alpha=1.25, N=14, g=5, workspace=ws)
     torch.cuda.synchronize()
 
-    part = idist.Partition(spec, ext, world, rank, "a", "b")
-    sa, sb = part.shard_start(0), part.shard_start(1)
-    ia = [slice(sa.get(c, 0), sa.get(c, 0) + e) for c, e in zip("kjbc", part.shard_shape(0))]
-    ib = [slice(sb.get(c, 0), sb.get(c, 0) + e) for c, e in zip("kiac", part.shard_shape(1))]
-    shard_a, shard_b = dA[tuple(ia)].contiguous(), dB[tuple(ib)].contiguous()
-    tile = tuple(slice(part.start.get(c, 0), part.start.get(c, 0) + part.local[c]) for c in "abij")
-    want = full[tile].contiguous()
-    groups = idist.make_groups(world, dist)
     failures = []
     variants = [dict(exchange="residues", push="kernel"), dict(exchange="residues", push="kernel", push_ctas=4),
                 dict(exchange="residues", push="copy"), dict(exchange="residues", push="copy", store_push=0),
                 dict(exchange="residues", push="kernel", store_push=1),
                 dict(exchange="residues", push="copy", sync="barrier"), dict(exchange="fp64"),
                 dict(exchange="pieces")]
-    for kw in variants:
-        for g in (5, 14):
-            rc = idist.RankContraction(part, N=14, g=g, dist=dist, groups=groups, **kw)
-            C = torch.full(rc.tile_shape, 7.0, dtype=torch.float64, device=dev)
-            for stepno in range(2):
-                C.fill_(7.0)
-                rc(shard_a, shard_b, C, alpha=1.25, beta=0.0)
-                torch.cuda.synchronize()
+    # the default grid with every variant; on 4 GPUs also the one-axis grids, where a slab has four
+    # producers (three pieces arrive from other ranks, as on a 2 x 4 grid of 8 GPUs)
+    runs = [(None, variants, (5, 14))]
+    if world == 4:
+        few = [dict(exchange="pieces"), dict(exchange="residues", push="copy"), dict(exchange=None)]
+        runs += [((1, 4), few, (5,)), ((4, 1), few, (7,))]
+    for grid, kinds, gs in runs:
+        part = idist.Partition(spec, ext, world, rank, "a", "b", grid)
+        sa, sb = part.shard_start(0), part.shard_start(1)
+        ia = [slice(sa.get(c, 0), sa.get(c, 0) + e) for c, e in zip("kjbc", part.shard_shape(0))]
+        ib = [slice(sb.get(c, 0), sb.get(c, 0) + e) for c, e in zip("kiac", part.shard_shape(1))]
+        shard_a, shard_b = dA[tuple(ia)].contiguous(), dB[tuple(ib)].contiguous()
+        tile = tuple(slice(part.start.get(c, 0), part.start.get(c, 0) + part.local[c]) for c in "abij")
+        want = full[tile].contiguous()
+        groups = idist.make_groups(world, dist, grid)
+        for kw in kinds:
+            for g in gs:
+                rc = idist.RankContraction(part, N=14, g=g, dist=dist, groups=groups, **kw)
+                C = torch.full(rc.tile_shape, 7.0, dtype=torch.float64, device=dev)
+                for stepno in range(2):
+                    C.fill_(7.0)
+                    rc(shard_a, shard_b, C, alpha=1.25, beta=0.0)
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    same = torch.equal(C.reshape(want.shape).view(torch.int64), want.view(torch.int64))
+                    err = rc.device_error()
+                    if not same or err:
+                        failures.append((grid, kw, g, stepno, bool(same), int(err)))
                 dist.barrier()
-                same = torch.equal(C.reshape(want.shape).view(torch.int64), want.view(torch.int64))
-                err = rc.device_error()
-                if not same or err:
-                    failures.append((kw, g, stepno, bool(same), int(err)))
-            dist.barrier()
-            rc.close()
+                rc.close()
     bad = torch.tensor([len(failures)], dtype=torch.int64, device=dev)
     dist.all_reduce(bad)
     if failures:
