@@ -68,8 +68,26 @@ def main(argv=None):
     L = lib.lib
     dev = torch.device("cuda", torch.cuda.current_device())
     spec = "bik,bkj->bij"
-    rows = {c: [] for c in ("scale", "res", "gemm", "crt", "direct", "beta", "pack")}
+    rows = {c: [] for c in ("scale", "res", "gemm", "crt", "direct", "beta", "pack", "kf")}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    # small contractions: one fused launch (phase tag 7)
+    for (b, m, n, k) in ((1, 40, 2048, 48), (1, 96, 96, 96), (1, 256, 256, 64), (4, 128, 128, 32),
+                         (1, 512, 512, 128), (1, 64, 64, 16), (1, 300, 200, 100), (16, 64, 96, 120)):
+        A = torch.rand((b, m, k), dtype=torch.float64, device=dev) * 2 - 1
+        B = torch.rand((b, k, n), dtype=torch.float64, device=dev) * 2 - 1
+        Cd = torch.zeros((b, m, n), dtype=torch.float64, device=dev)
+        for N in ((14,) if args.quick else (14, 8, 20)):
+            pred = host.predict(spec, dict(b=b, i=m, j=n, k=k), N=N)
+            ph = {p["phase"]: p for p in pred["phases"]}
+            if "KF fused" not in ph:
+                continue
+            plan = imd.Plan(spec, A, B, Cd, N=N, lib=lib)
+            ws = torch.empty(max(plan.workspace_bytes, 1), dtype=torch.uint8, device=dev)
+            t = measure(lambda: (flush.fill_(1), plan.contract(A, B, Cd, workspace=ws)), L, (1, 7), args.steps)
+            rows["kf"].append((t[7], [ph["KF fused"]["x"][2], ph["KF fused"]["x"][5]]))
+            plan.close()
+            print(f"measured fused b={b} m={m} n={n} k={k} N={N}: {t[7] / 1e3:.1f}us", file=sys.stderr)
 
     last = None
     for (b, m, n, k, N, g) in shapes(args.quick):
@@ -79,6 +97,8 @@ def main(argv=None):
             Cd = torch.zeros((b, m, n), dtype=torch.float64, device=dev)
             last = (b, m, n, k)
         ext = dict(b=b, i=m, j=n, k=k)
+        if host.lowering(spec, ext, N=N, g=g)["fused"]:
+            continue                      # measured above
         plan = imd.Plan(spec, A, B, Cd, N=N, g=g, lib=lib)
         ws = torch.empty(max(plan.workspace_bytes, 1), dtype=torch.uint8, device=dev)
 
@@ -146,8 +166,13 @@ def main(argv=None):
     for i in range(96):
         P[i] = 0.0
     dram_ns = 1e9 / 6.5e12      # ns per DRAM byte at the measured copy bandwidth
-    K0, KL, PACK, K4, K5, DIRECT, BETA, CALL = 0, 12, 18, 24, 48, 54, 60, 66
+    K0, KF, KL, PACK, K4, K5, DIRECT, BETA, CALL = 0, 6, 12, 18, 24, 48, 54, 60, 66
     P[CALL + 1] = launch
+    if rows["kf"]:
+        # the fused launch has a fixed cost of its own on top of a launch (its chain of dependent
+        # cold loads: row offsets, rows, C)
+        P[KF + 0], P[KF + 2], P[KF + 5] = fit([r[0] for r in rows["kf"]], [[1.0] + r[1] for r in rows["kf"]],
+                                              [1] * len(rows["kf"]))
     n = len(rows["crt"])
     P[KL + 2] = fit([rows["scale"][i][0] for i in range(n)],
                     [[rows["scale"][i][1][2]] for i in range(n)], [rows["scale"][i][1][0] for i in range(n)])[0]
@@ -196,6 +221,11 @@ def main(argv=None):
             ratios[key].append(m_ / p_)
         tot.append(((sc + rs + gm + cr) * 1e-9, sum(meas) / (sc + rs + gm + cr)))
     ratios["k0"] = ratios["kl"]
+    if rows["kf"]:
+        ratios["kf"] = [r[0] / (launch + P[KF + 0] + r[1][0] * P[KF + 2] + r[1][1] * P[KF + 5])
+                        for r in rows["kf"]]
+        for r, q in zip(rows["kf"], ratios["kf"]):
+            print(f"fused: measured {r[0] / 1e3:.1f} us, measured/predicted {q:.3f}", file=sys.stderr)
     if rows["direct"]:
         ratios["direct"] = [r[0] / (2 * launch + r[1][1] * P[DIRECT + 2]) for r in rows["direct"]]
         ratios["beta"] = [r[0] / (2 * launch + r[1][1] * P[BETA + 1]) for r in rows["beta"]]
@@ -209,7 +239,7 @@ def main(argv=None):
     cal.gpu = torch.cuda.get_device_name(dev).encode()[:63]
     cal.sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     cal.date = datetime.date.today().isoformat().encode()
-    cal.notes = (f"{len(rows['crt'])} contractions, {len(rows['pack'])} packs; NNLS per class on "
+    cal.notes = (f"{len(rows['crt'])} contractions, {len(rows['kf'])} fused, {len(rows['pack'])} packs; NNLS per class on "
                  "CUDA-event phase times, L2 flushed between calls").encode()[:127]
     text = host.calib_format(cal)
     host.calib_parse(text)      # must parse back

@@ -103,7 +103,7 @@ struct Hooks {
 };
 const Hooks& hooks();
 // Phase boundary of a call (tags: 1 vectors + scale, 2 quantise, 3 GEMM, 4 CRT, 5 degenerate path,
-// 6 imd_pack): records an event in the instrumented library, nothing in the production one.
+// 6 imd_pack, 7 the one fused launch of a small contraction): records an event in the instrumented library, nothing in the production one.
 void phase_mark(int tag, cudaStream_t stream);
 // Benchmark hook: int8 ops per second of back-to-back tcgen05.mma.kind::i8 with no loads.
 double mma_probe_tops(int pair, int sms);

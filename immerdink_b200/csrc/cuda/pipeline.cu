@@ -727,7 +727,7 @@ imd_status_t enqueue_contract(const imd_plan_st& plan, double alpha, const doubl
     sp.group = static_cast<int32_t>(group);
     const int64_t tiles = ((e.m + kSmTM - 1) / kSmTM) * ((e.n + kSmTN - 1) / kSmTN) * e.b;
     k_small<<<static_cast<unsigned int>(tiles), kSmThreads, small_smem_bytes(sp.kh, sp.group, e.N), stream>>>(sp);
-    phase_mark(4, stream);
+    phase_mark(7, stream);
     return launched() ? IMD_STATUS_SUCCESS : IMD_STATUS_CUDA_ERROR;
   }
 

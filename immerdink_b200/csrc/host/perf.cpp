@@ -135,6 +135,17 @@ void contract_phases(const Analysis& an, const ExecPlan& e, int32_t flags, int s
     p.ops = 2.0 * outputs * d(e.k);
     p.peak = 2;
     p.x[0] = 1, p.x[1] = p.bytes, p.x[2] = p.ops;
+  } else if (e.small()) {
+    // one fused launch: every 32 x 32 tile quantises its 64 rows of kh entries for N moduli,
+    // multiplies them and runs the CRT of its outputs
+    Phase& p = P->add(IMD_PERF_PHASE_KF, IMD_PERF_CLASS_KF, 1);
+    const double tiles = d(ceil_div(e.m, 32)) * d(ceil_div(e.n, 32)) * d(e.b);
+    const double kh = d(ceil_div(e.k, 32) * 32);
+    p.bytes = 8.0 * d(e.b) * d(e.k) * (d(e.m) + d(e.n)) + c_bytes;
+    p.ops = 2.0 * d(e.N) * outputs * d(e.k);
+    p.x[0] = 1, p.x[1] = p.bytes, p.x[2] = tiles * 64.0 * kh * d(e.N), p.x[3] = tiles * 1024.0 * d(e.N);
+    // what one SM does one tile after the other (a tile is not shared between SMs)
+    p.x[5] = d(ceil_div(static_cast<int64_t>(tiles), std::max(sms, 1))) * 64.0 * kh * d(e.N);
   } else {
     const int64_t groups = ceil_div(e.N, e.g);
     const int64_t rows[2] = {e.m, e.n}, rows_pad[2] = {e.m, e.n_hat};
