@@ -163,3 +163,24 @@ def test_push_order_serves_every_consumer_from_one_producer_per_turn():
                 turns.setdefault(t, []).append(peers[j])
         for t, served in turns.items():
             assert sorted(served) == list(range(sharers)), (sharers, t, served)
+
+
+def test_default_exchange_by_grid_and_arrival_order_of_pieces():
+    """Residue planes up to four ranks, FP64 pieces once a slab has four producers (the default
+    grid of 8 ranks, the one-axis grids of 4); a consumer waits for the pieces of the other
+    producers in the order in which push_order makes them arrive."""
+    from immerdink_b200.dist import Partition, default_exchange, push_order
+    ext = dict(a=64, b=64, c=8, i=2, j=2, k=2)
+    spec = "kjbc,kiac->abij"
+    want = {(1, None): "fp64", (2, None): "residues", (4, None): "residues", (8, None): "pieces",
+            (4, (1, 4)): "pieces", (4, (4, 1)): "pieces", (2, (2, 1)): "residues"}
+    for (world, grid), name in want.items():
+        assert default_exchange(Partition(spec, ext, world, 0, "a", "b", grid)) == name
+    # consumer at position c of a slab with n producers: in turn t it is served by producer c - 1 - t
+    for n in (2, 4):
+        for c in range(n):
+            arrival = [(c - 1 - t) % n for t in range(n - 1)]
+            for turn, producer in enumerate(arrival):
+                others = [q for q in range(n) if q != producer]
+                served = [others[j] for j in push_order(others, producer, n)]
+                assert served[turn] == c
