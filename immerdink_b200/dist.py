@@ -273,6 +273,7 @@ class RankContraction:
             self.plan = _dev.Plan(self.spec, *lays, N=N, g=g, rounding=rounding,
                                   packs=tuple(self.slab), lib=lib)
             self.pack_ws = [nbytes(pk.workspace_bytes) for pk in self.piece]
+            self.pack_ws2 = [nbytes(pk.workspace_bytes) for pk in self.piece]   # packs on the side stream
             self.slab_rows = [pk.layout["r"] for pk in self.slab]
             # this rank's piece inside each slab: its position in the group that shares the slab
             self.pos = (part.ra, part.rb)
@@ -677,11 +678,20 @@ class RankContraction:
         sent = push.record_event()
         self._mark("pushed", push)
 
-        def pack(x, src, position):
+        # The packs alternate between the main stream and a side stream: a pack of 1000 rows fills
+        # the GPU for one wave and a third, two of them running side by side fill each other's tail
+        lanes = [(main, s, self.pack_ws), (self.side, self.side.cuda_stream, self.pack_ws2)]
+        self.side.wait_event(main.record_event())
+        turn = [0]
+
+        def pack(x, src, position, wait_for=None):
+            stream, handle, wss = lanes[turn[0] % 2]
+            turn[0] += 1
+            if wait_for is not None:
+                _dev_wait([wait_for], tick, stream=handle, lib=self.lib)
             rp = self.piece[x].layout["r"]
             self.piece[x].scatter_ptr(src, self.slab_rows[x], position * rp, self.dests[x][:1],
-                                      self.slab[x].pack_bytes, self.pack_ws[x].data_ptr(),
-                                      self.pack_ws[x].numel(), s)
+                                      self.slab[x].pack_bytes, wss[x].data_ptr(), wss[x].numel(), handle)
 
         for x in order:                       # own pieces: nothing to wait for
             pack(x, shards[x].data_ptr(), self.pos[x])
@@ -690,8 +700,9 @@ class RankContraction:
             n = pieces_of[x]
             for t in range(n - 1):
                 position = (self.pos[x] - 1 - t) % n
-                _dev_wait([self.flags + word(x, position)], tick, stream=s, lib=self.lib)
-                pack(x, self.fp64_dests[x][0] + position * piece_bytes[x], position)
+                pack(x, self.fp64_dests[x][0] + position * piece_bytes[x], position,
+                     wait_for=self.flags + word(x, position))
+        main.wait_event(self.side.record_event())
         self._mark("packed all", main)
         # the own pieces at their place in the own FP64 slabs: only the native path of flagged rows
         # reads them, so they are copied only if a row flag of the slabs is set
