@@ -656,8 +656,8 @@ class RankContraction:
         pieces_of = (self.part.pieces_b, self.part.pieces_a)     # pieces of the slab of A, of B
         piece_bytes = [shards[x].numel() * 8 for x in (0, 1)]
 
-        def copy(dst, src, nbytes):
-            err, = rt.cudaMemcpyAsync(dst, src, nbytes, kind, push.cuda_stream)
+        def copy(dst, src, nbytes, st):
+            err, = rt.cudaMemcpyAsync(dst, src, nbytes, kind, st.cuda_stream)
             if err != rt.cudaError_t.cudaSuccess:
                 raise RuntimeError(f"cudaMemcpyAsync to a peer: {err}")
 
@@ -667,14 +667,22 @@ class RankContraction:
         self._mark("begin", main)
         self._barrier()                       # every rank is done with the previous step's slabs
         self._mark("all ranks in", main)
-        push.wait_event(main.record_event())
-        # the slab with more consumers first; every producer serves the consumer after itself first
+        start = main.record_event()
+        for st in self.push_streams:
+            st.wait_event(start)
+        # the slab with more consumers first; every producer serves the consumer after itself first;
+        # the copies go to the push streams in turn (a piece and its flag word on the same one)
         order = (1, 0) if self.part.pb > self.part.pa else (0, 1)
+        nth = 0
         for x in order:
             for j in self.push_order[x]:
+                st = self.push_streams[nth % len(self.push_streams)]
+                nth += 1
                 copy(self.fp64_dests[x][1 + j] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(),
-                     piece_bytes[x])
-                copy(self.flag_dests[x][j] + word(x, self.pos[x]), self.values.data_ptr() + 4 * tick, 4)
+                     piece_bytes[x], st)
+                copy(self.flag_dests[x][j] + word(x, self.pos[x]), self.values.data_ptr() + 4 * tick, 4, st)
+        for st in self.push_streams[1:]:
+            push.wait_event(st.record_event())
         sent = push.record_event()
         self._mark("pushed", push)
 
