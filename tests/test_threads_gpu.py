@@ -90,6 +90,7 @@ def test_eight_threads_shared_and_own_plans():
     ("ik,jk->ij", dict(i=300, j=260, k=500), 14, 14),       # both fused, one group
     ("ik,kj->ij", dict(i=64, j=48, k=131500), 5, 2),        # two K chunks, three groups
     ("ik,kj->ij", dict(i=40, j=30, k=1), 14, 0),            # native path
+    ("ijk,kl->lij", dict(i=64, j=32, k=48, l=40), 14, 0),   # small: the vectors and one fused launch
 ])
 def test_kernel_launches_equal_the_lowering(spec, shape, N, g):
     """A stream capture of one imd_contract holds exactly kernel_launches kernel nodes."""
