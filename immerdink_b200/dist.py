@@ -148,12 +148,12 @@ def gather(part, shard_a, shard_b, out_a, out_b, groups, dist):
 
 def default_exchange(part):
     """The exchange RankContraction uses when none is named: residue planes group by group up to
-    four ranks (measured: 3.74 ms on 2 and 2.00 ms on 4 B200 against 2.04 ms for the pieces on 4);
+    four ranks (measured: 3.53 ms on 2 and 2.00 ms on 4 B200 against 3.53 and 2.02 ms for the pieces);
     FP64 pieces once a slab has four producers: the planes of three other producers reach a
     consumer through one copy-engine stream at about 350 GB/s while the GEMM runs, which bounds
-    the step (1.0 ms of copies for 0.6 ms of GEMM on 8 B200), whereas the pieces are 8 bytes per
-    entry instead of 14, travel in a few large copies before any GEMM starts, and their
-    quantisation at the consumer costs less than the difference."""
+    the step (1.49 ms on 8 B200), whereas the pieces are 8 bytes per entry instead of 14, travel in
+    a few large copies before any GEMM starts, and their quantisation at the consumer costs less
+    than the difference (1.37 ms)."""
     if part.world == 1:
         return "fp64"
     return "pieces" if max(part.pa, part.pb) >= 4 else "residues"
