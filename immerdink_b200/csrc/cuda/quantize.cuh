@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm) k_quantize(const __gri
     if (live && K0 + step < kend && c + 1 >= staged) load8(p, base, K0 + step + 8 * lane, raw);
     const bool in_k = K0 + kofs < p.k_hat;
     int64_t at = out0 + K0;
-#pragma unroll 2
+#pragma unroll 1  // measured: 1.10 ms against 1.13 (unroll 2) and 1.11 (unroll 4) at the 8000 x 8000 shape
     for (int s = 0; s < slots; ++s, at += 2 * plane) {
       const uint32_t b0 = s_b[0][s][lane], b1 = s_b[1][s][lane];
       const float inv = s_inv[s][half];
