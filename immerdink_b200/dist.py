@@ -237,7 +237,7 @@ class RankContraction:
 
     def __init__(self, part, *, N, g=0, rounding="RN", dist=None, groups=None, lib=None,
                  exchange=None, push_streams=1, sync="flags", store_push="auto", push="copy",
-                 push_ctas=0):
+                 push_ctas=0, carrier="copy"):
         import torch
         from . import device as _dev
         self._torch, self.part, self.dist = torch, part, dist
@@ -274,6 +274,7 @@ class RankContraction:
                                   packs=tuple(self.slab), lib=lib)
             self.pack_ws = [nbytes(pk.workspace_bytes) for pk in self.piece]
             self.pack_ws2 = [nbytes(pk.workspace_bytes) for pk in self.piece]   # packs on the side stream
+            self.gather_stream = torch.cuda.Stream(dev)
             self.slab_rows = [pk.layout["r"] for pk in self.slab]
             # this rank's piece inside each slab: its position in the group that shares the slab
             self.pos = (part.ra, part.rb)
@@ -295,6 +296,12 @@ class RankContraction:
             if push not in ("kernel", "copy"):
                 raise ValueError("push must be 'kernel' or 'copy'")
             self.push, self.push_ctas = push, int(push_ctas)
+            # carrier of the FP64 pieces in the piece exchange: "copy" = one peer copy per piece and
+            # consumer on the copy engines, announced by flag words; "nccl" = one all-gather per
+            # operand inside the group that shares its slab (side stream)
+            if carrier not in ("copy", "nccl"):
+                raise ValueError("carrier must be 'copy' or 'nccl'")
+            self.carrier = carrier
             if push == "kernel" and sync != "flags":
                 raise ValueError("push='kernel' announces by flag words: sync must be 'flags'")
             if store_push == "auto":   # one copy-engine stream carries about 350 GB/s in 8 MB copies: with
@@ -668,23 +675,40 @@ class RankContraction:
         self._barrier()                       # every rank is done with the previous step's slabs
         self._mark("all ranks in", main)
         start = main.record_event()
-        for st in self.push_streams:
-            st.wait_event(start)
-        # the slab with more consumers first; every producer serves the consumer after itself first;
-        # the copies go to the push streams in turn (a piece and its flag word on the same one)
         order = (1, 0) if self.part.pb > self.part.pa else (0, 1)
-        nth = 0
-        for x in order:
-            for j in self.push_order[x]:
-                st = self.push_streams[nth % len(self.push_streams)]
-                nth += 1
-                copy(self.fp64_dests[x][1 + j] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(),
-                     piece_bytes[x], st)
-                copy(self.flag_dests[x][j] + word(x, self.pos[x]), self.values.data_ptr() + 4 * tick, 4, st)
-        for st in self.push_streams[1:]:
-            push.wait_event(st.record_event())
-        sent = push.record_event()
-        self._mark("pushed", push)
+        gathered = [None, None]
+        if self.carrier == "nccl" and self.part.world > 1:
+            # one all-gather per operand inside the group that shares its slab, the larger group
+            # first; the pieces land at their place in the gathered FP64 slabs (the own one too)
+            cols, rows = self.groups
+            grp = (cols[self.part.rb], rows[self.part.ra])
+            slabs = (self.A, self.B)
+            self.gather_stream.wait_event(start)
+            with torch.cuda.stream(self.gather_stream):
+                for x in order:
+                    if grp[x] is None:
+                        slabs[x][0].copy_(shards[x], non_blocking=True)
+                    else:
+                        self.dist.all_gather_into_tensor(slabs[x].view(-1), shards[x].view(-1), group=grp[x])
+                    gathered[x] = self.gather_stream.record_event()
+            sent = gathered[order[1]]
+        else:
+            for st in self.push_streams:
+                st.wait_event(start)
+            # the slab with more consumers first; every producer serves the consumer after itself
+            # first; the copies go to the push streams in turn (a piece and its flag word on the same one)
+            nth = 0
+            for x in order:
+                for j in self.push_order[x]:
+                    st = self.push_streams[nth % len(self.push_streams)]
+                    nth += 1
+                    copy(self.fp64_dests[x][1 + j] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(),
+                         piece_bytes[x], st)
+                    copy(self.flag_dests[x][j] + word(x, self.pos[x]), self.values.data_ptr() + 4 * tick, 4, st)
+            for st in self.push_streams[1:]:
+                push.wait_event(st.record_event())
+            sent = push.record_event()
+        self._mark("pushed", self.gather_stream if gathered[0] is not None else push)
 
         # The packs alternate between the main stream and a side stream: a pack of 1000 rows fills
         # the GPU for one wave and a third, two of them running side by side fill each other's tail
@@ -695,7 +719,9 @@ class RankContraction:
         def pack(x, src, position, wait_for=None):
             stream, handle, wss = lanes[turn[0] % 2]
             turn[0] += 1
-            if wait_for is not None:
+            if wait_for is not None and gathered[x] is not None:
+                stream.wait_event(gathered[x])            # the operand's all-gather has completed
+            elif wait_for is not None:
                 _dev_wait([wait_for], tick, stream=handle, lib=self.lib)
             rp = self.piece[x].layout["r"]
             self.piece[x].scatter_ptr(src, self.slab_rows[x], position * rp, self.dests[x][:1],
@@ -718,7 +744,8 @@ class RankContraction:
                  self.slab[x].layout["b"] * self.slab_rows[x]) for x in (0, 1)]
         own = [(self.fp64_dests[x][0] + self.pos[x] * piece_bytes[x], shards[x].data_ptr(), piece_bytes[x])
                for x in (0, 1)]
-        _dev_copy_if(rows, own, stream=s, lib=self.lib)
+        if gathered[0] is None:
+            _dev_copy_if(rows, own, stream=s, lib=self.lib)
         main.wait_event(sent)                 # the shards may change once the step's work is done
         self.plan.contract_ptr(alpha, self.A.data_ptr(), self.B.data_ptr(), beta, C.data_ptr(),
                                self.ws.data_ptr(), self.ws.numel(), s, packed=tuple(self.packed))

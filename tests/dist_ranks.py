@@ -44,12 +44,13 @@ def main():
                 dict(exchange="residues", push="copy"), dict(exchange="residues", push="copy", store_push=0),
                 dict(exchange="residues", push="kernel", store_push=1),
                 dict(exchange="residues", push="copy", sync="barrier"), dict(exchange="fp64"),
-                dict(exchange="pieces")]
+                dict(exchange="pieces"), dict(exchange="pieces", carrier="nccl")]
     # the default grid with every variant; on 4 GPUs also the one-axis grids, where a slab has four
     # producers (three pieces arrive from other ranks, as on a 2 x 4 grid of 8 GPUs)
     runs = [(None, variants, (5, 14))]
     if world == 4:
-        few = [dict(exchange="pieces"), dict(exchange="residues", push="copy"), dict(exchange=None)]
+        few = [dict(exchange="pieces"), dict(exchange="pieces", carrier="nccl"),
+               dict(exchange="residues", push="copy"), dict(exchange=None)]
         runs += [((1, 4), few, (5,)), ((4, 1), few, (7,))]
     for grid, kinds, gs in runs:
         part = idist.Partition(spec, ext, world, rank, "a", "b", grid)
